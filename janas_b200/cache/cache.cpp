@@ -90,6 +90,11 @@ size_t KVGroup::entry_bytes() const {
            dtype_size(k.dt);
 }
 
+size_t KVGroup::v_entry_bytes() const {
+    return (size_t)pool.n_pages() * (size_t)spec.num_kv_heads * PAGE * (size_t)spec.value_dim() *
+           dtype_size(v.dt);
+}
+
 int KVGroup::first_needed_page(long long next_pos) const {
     if (!spec.window) return 0;
     return (int)(std::max(0ll, next_pos + 1 - spec.window) / PAGE);
@@ -152,12 +157,15 @@ Cache::Cache(const std::vector<KVSpec> &kv_specs, const std::vector<StateSpec> &
         grp->k.dt = grp->v.dt = dt;
         std::vector<long long> shape = {(long long)g.second.size(), n_pages, g.first.num_kv_heads, PAGE,
                                         g.first.head_dim};
+        std::vector<long long> v_shape = shape;
+        v_shape.back() = g.first.value_dim();
         if (dev) {
             dev->make_current();
             grp->k = dev->tensor(dt, shape, true);
-            grp->v = dev->tensor(dt, shape, true);
+            grp->v = dev->tensor(dt, v_shape, true);
         } else {
-            grp->k.shape = grp->v.shape = shape;
+            grp->k.shape = shape;
+            grp->v.shape = v_shape;
         }
         for (int e : g.second) group_of[e] = grp;
     }
@@ -341,8 +349,10 @@ size_t Cache::bytes() const {
     size_t b = 0;
     for (auto &g : groups) {
         size_t n = dtype_size(dtype);
+        size_t nv = n;
         for (auto s : g->k.shape) n *= (size_t)s;
-        b += 2 * n;
+        for (auto s : g->v.shape) nv *= (size_t)s;
+        b += n + nv;
     }
     return b;
 }
@@ -379,6 +389,7 @@ Json Cache::describe() const {
         Json j = Json::object();
         j.set("num_kv_heads", g->spec.num_kv_heads);
         j.set("head_dim", g->spec.head_dim);
+        j.set("v_head_dim", g->spec.value_dim());
         j.set("window", g->spec.window);
         Json es = Json::array();
         for (int e : g->entries) es.push(e);

@@ -7,7 +7,8 @@
 // same number of KV heads and head size, and either all positions or a window of
 // them).  Every group has a pool and tensors of its own:
 //
-//     K, V: [entries of the group, pages, kv_heads, PAGE, head_dim]
+//     K, V: [entries of the group, pages, kv_heads, PAGE, head_dim]   (V with its own
+//           head size where a mixer's values are not as long as its keys)
 //
 // A group with a window gives pages back as soon as no later token can see them,
 // so a long sequence holds only about window / PAGE + 1 pages there.
@@ -86,9 +87,12 @@ private:
 // otherwise only the last `window` positions can be read again.
 struct KVSpec {
     int num_kv_heads = 0, head_dim = 0, window = 0;
+    int v_head_dim = 0;     // the values' head size where it is not the keys'; 0: the same
     bool none() const { return num_kv_heads == 0; }
+    int value_dim() const { return v_head_dim > 0 ? v_head_dim : head_dim; }
     bool operator==(const KVSpec &o) const {
-        return num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && window == o.window;
+        return num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && window == o.window &&
+               value_dim() == o.value_dim();
     }
 };
 
@@ -113,9 +117,10 @@ public:
     // per slot: the page of every page index (absolute position / PAGE), -1 once released
     std::vector<std::vector<int>> pages;
 
-    size_t entry_bytes() const;            // bytes of one entry's K (or V)
+    size_t entry_bytes() const;            // bytes of one entry's K
+    size_t v_entry_bytes() const;          // bytes of one entry's V
     void *k_of(int entry) const { return (char *)k.ptr + (size_t)index.at(entry) * entry_bytes(); }
-    void *v_of(int entry) const { return (char *)v.ptr + (size_t)index.at(entry) * entry_bytes(); }
+    void *v_of(int entry) const { return (char *)v.ptr + (size_t)index.at(entry) * v_entry_bytes(); }
     int first_needed_page(long long next_pos) const;
     void extend(int slot, long long end);
     void release_unseen(int slot, long long next_pos);

@@ -70,14 +70,56 @@ class LayerSpec:
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]        # None: the layer has no feed-forward (and no ffn_norm)
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: Optional[PartSpec]
     prefix: str
     mixer_name: str = "self_attn"
     ffn_name: str = "mlp"
     mixer_norm_name: str = "input_layernorm"
     ffn_norm_name: str = "post_attention_layernorm"
+    # norms on the sublayers' results, for the arrangements that have them
+    post_mixer_norm: Optional[PartSpec] = None
+    post_ffn_norm: Optional[PartSpec] = None
+    post_mixer_norm_name: str = "post_mixer_norm"
+    post_ffn_norm_name: str = "post_ffn_norm"
+    # the arrangement's own constants and the names of tensors it owns
+    block_params: Mapping[str, Any] = field(default_factory=dict)
+
+    def __hash__(self) -> int:
+        return hash((self.block, self.mixer, self.feed_forward, self.mixer_norm, self.ffn_norm,
+                     self.prefix, json.dumps(_plain(self.block_params), sort_keys=True)))
+
+    def to_json(self) -> Dict[str, Any]:
+        none = {"kind": "", "params": {}}
+        d = {"block": self.block, "mixer": self.mixer.to_json(),
+             "feed_forward": self.feed_forward.to_json() if self.feed_forward else none,
+             "mixer_norm": self.mixer_norm.to_json(),
+             "ffn_norm": self.ffn_norm.to_json() if self.ffn_norm else none,
+             "prefix": self.prefix, "mixer_name": self.mixer_name, "ffn_name": self.ffn_name,
+             "mixer_norm_name": self.mixer_norm_name, "ffn_norm_name": self.ffn_norm_name,
+             "post_mixer_norm_name": self.post_mixer_norm_name,
+             "post_ffn_norm_name": self.post_ffn_norm_name}
+        if self.post_mixer_norm:
+            d["post_mixer_norm"] = self.post_mixer_norm.to_json()
+        if self.post_ffn_norm:
+            d["post_ffn_norm"] = self.post_ffn_norm.to_json()
+        if self.block_params:
+            d["block_params"] = _plain(self.block_params)
+        return d
+
+    @staticmethod
+    def from_json(l: Mapping[str, Any]) -> "LayerSpec":
+        def part(key):
+            v = l.get(key)
+            return PartSpec.from_json(v) if v and v.get("kind") else None
+        return LayerSpec(
+            l["block"], PartSpec.from_json(l["mixer"]), part("feed_forward"),
+            PartSpec.from_json(l["mixer_norm"]), part("ffn_norm"), l["prefix"],
+            l["mixer_name"], l["ffn_name"], l["mixer_norm_name"], l["ffn_norm_name"],
+            part("post_mixer_norm"), part("post_ffn_norm"),
+            l.get("post_mixer_norm_name", "post_mixer_norm"),
+            l.get("post_ffn_norm_name", "post_ffn_norm"), l.get("block_params") or {})
 
 
 @dataclass(frozen=True)
@@ -103,30 +145,30 @@ class ModelSpec:
     embedding_name: str = "model.embed_tokens.weight"
     final_norm_name: str = "model.norm"
     head_name: str = "lm_head.weight"
+    position_table_name: str = ""      # a table of learned position vectors; "": none
+    logit_scale: float = 1.0
 
     def to_json(self) -> Dict[str, Any]:
-        return {
+        d = {
             "architecture": self.architecture, "hidden_size": self.hidden_size,
             "vocab_size": self.vocab_size, "max_positions": self.max_positions,
-            "layers": [{"block": l.block, "mixer": l.mixer.to_json(),
-                        "feed_forward": l.feed_forward.to_json(),
-                        "mixer_norm": l.mixer_norm.to_json(), "ffn_norm": l.ffn_norm.to_json(),
-                        "prefix": l.prefix, "mixer_name": l.mixer_name, "ffn_name": l.ffn_name,
-                        "mixer_norm_name": l.mixer_norm_name, "ffn_norm_name": l.ffn_norm_name}
-                       for l in self.layers],
+            "layers": [l.to_json() for l in self.layers],
             "run_order": [{"layer": e.layer, "cache_of": e.cache_of} for e in self.run_order],
             "final_norm": self.final_norm.to_json(), "tie_embeddings": self.tie_embeddings,
             "embedding_name": self.embedding_name, "final_norm_name": self.final_norm_name,
             "head_name": self.head_name}
+        if self.position_table_name:
+            d["position_table_name"] = self.position_table_name
+        if self.logit_scale != 1.0:
+            d["logit_scale"] = self.logit_scale
+        return d
 
     @staticmethod
     def from_json(d: Mapping[str, Any]) -> "ModelSpec":
-        layers = tuple(LayerSpec(
-            l["block"], PartSpec.from_json(l["mixer"]), PartSpec.from_json(l["feed_forward"]),
-            PartSpec.from_json(l["mixer_norm"]), PartSpec.from_json(l["ffn_norm"]), l["prefix"],
-            l["mixer_name"], l["ffn_name"], l["mixer_norm_name"], l["ffn_norm_name"])
-            for l in d["layers"])
+        layers = tuple(LayerSpec.from_json(l) for l in d["layers"])
         return ModelSpec(
+            position_table_name=d.get("position_table_name", ""),
+            logit_scale=d.get("logit_scale", 1.0),
             architecture=d["architecture"], hidden_size=d["hidden_size"],
             vocab_size=d["vocab_size"], max_positions=d["max_positions"], layers=layers,
             run_order=tuple(RunEntry(e["layer"], e["cache_of"]) for e in d["run_order"]),
@@ -171,11 +213,44 @@ class Qwen3Config:
         return ModelSpec.from_json(self._spec)
 
 
+@dataclass(frozen=True)
+class ZuzelornConfig:
+    """The Zuzelorn decoder's ``config.json`` keys, as the library read them."""
+    vocab: int
+    width: int
+    max_positions: int
+    norm_eps: float
+    logit_scale: float
+    layers: Tuple[Mapping[str, Any], ...]     # each: type, mixer {...}, mlp {...} or None
+    eos_token_ids: Tuple[int, ...] = ()
+    architecture: str = "Zuzelorn"
+    _json: Mapping[str, Any] = field(default_factory=dict, compare=False, repr=False)
+    _spec: Mapping[str, Any] = field(default_factory=dict, compare=False, repr=False)
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "ZuzelornConfig":
+        return _wrap(_call("config.parse", config=dict(d)))
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dict(self._json)
+
+    def to_model_spec(self) -> ModelSpec:
+        return ModelSpec.from_json(self._spec)
+
+    def __hash__(self) -> int:
+        return hash(json.dumps(self.to_dict(), sort_keys=True))
+
+
 def _wrap(r: Mapping[str, Any]):
     c = r["config"]
-    n = c["num_hidden_layers"]
+    if r["architecture"] == "Zuzelorn":
+        return ZuzelornConfig(
+            vocab=c["vocab"], width=c["width"], max_positions=c["max_positions"],
+            norm_eps=c["norm"]["eps"], logit_scale=c["logit_scale"], layers=tuple(c["layers"]),
+            eos_token_ids=tuple(r["eos_token_ids"]), _json=c, _spec=r["spec"])
     if r["architecture"] != "Qwen3ForCausalLM" and c.get("model_type") != "qwen3":
         raise ConfigError(f"no Python class for architecture {r['architecture']!r}")
+    n = c["num_hidden_layers"]
     return Qwen3Config(
         vocab_size=c["vocab_size"], hidden_size=c["hidden_size"],
         intermediate_size=c["intermediate_size"], num_hidden_layers=n,
@@ -203,4 +278,4 @@ def config_from_dir(model_dir: str):
 
 
 __all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config",
-           "config_from_dict", "config_from_dir", "known_architectures"]
+           "ZuzelornConfig", "config_from_dict", "config_from_dir", "known_architectures"]

@@ -32,7 +32,10 @@ void register_architecture(const std::string &name, const std::string &model_typ
 
 static Tables &ready() {
     static std::once_flag once;
-    std::call_once(once, [] { register_qwen3(); });
+    std::call_once(once, [] {
+        register_qwen3();
+        register_zuzelorn();
+    });
     return raw_tables();
 }
 
@@ -45,13 +48,15 @@ std::vector<std::string> known_architectures() {
 std::string architecture_name(const Json &d) {
     const Json &archs = d.get("architectures");
     if (archs.is_array() && archs.size() > 0 && archs[0].is_string()) return archs[0].as_string();
+    // a design that names itself with one word
+    if (d.get("architecture").is_string()) return d.get("architecture").as_string();
     const Json &mt = d.get("model_type");
     if (mt.is_string()) {
         auto &m = ready().by_model_type;
         auto it = m.find(mt.as_string());
         if (it != m.end()) return it->second;
     }
-    config_error("config.json names no architecture (architectures, model_type)");
+    config_error("config.json names no architecture (architectures, architecture, model_type)");
 }
 
 std::unique_ptr<ArchConfig> config_from_json(const Json &d) {

@@ -47,6 +47,9 @@ void ModelSpec::validate() const {
     if (hidden_size <= 0 || vocab_size <= 0 || max_positions <= 0)
         config_error("hidden_size, vocab_size and max_positions must be positive");
     if (layers.empty()) config_error("a model needs at least one layer");
+    for (size_t i = 0; i < layers.size(); i++)
+        if (layers[i].feed_forward.kind.empty() != layers[i].ffn_norm.kind.empty())
+            config_error(fmt("layer %zu: a feed-forward and its norm come together or not at all", i));
     if (run_order.empty()) config_error("the run order is empty");
     for (size_t at = 0; at < run_order.size(); at++) {
         const RunEntry &e = run_order[at];
@@ -78,6 +81,11 @@ Json ModelSpec::to_json() const {
         o.set("feed_forward", l.feed_forward.to_json());
         o.set("mixer_norm", l.mixer_norm.to_json());
         o.set("ffn_norm", l.ffn_norm.to_json());
+        if (!l.post_mixer_norm.kind.empty()) o.set("post_mixer_norm", l.post_mixer_norm.to_json());
+        if (!l.post_ffn_norm.kind.empty()) o.set("post_ffn_norm", l.post_ffn_norm.to_json());
+        if (l.block_params.size() > 0) o.set("block_params", l.block_params);
+        o.set("post_mixer_norm_name", l.post_mixer_norm_name);
+        o.set("post_ffn_norm_name", l.post_ffn_norm_name);
         o.set("prefix", l.prefix);
         o.set("mixer_name", l.mixer_name);
         o.set("ffn_name", l.ffn_name);
@@ -96,6 +104,8 @@ Json ModelSpec::to_json() const {
     j.set("run_order", ro);
     j.set("final_norm", final_norm.to_json());
     j.set("tie_embeddings", tie_embeddings);
+    if (!position_table_name.empty()) j.set("position_table_name", position_table_name);
+    if (logit_scale != 1.0) j.set("logit_scale", logit_scale);
     j.set("embedding_name", embedding_name);
     j.set("final_norm_name", final_norm_name);
     j.set("head_name", head_name);
@@ -104,6 +114,12 @@ Json ModelSpec::to_json() const {
 
 static std::string str_or(const Json &j, const char *k, const std::string &dflt) {
     return j.get(k).is_string() ? j.get(k).as_string() : dflt;
+}
+
+// an absent part: null, or a part whose kind is ""
+static PartSpec part_or_none(const Json &j) {
+    if (j.is_null()) return PartSpec();
+    return PartSpec::from_json(j);
 }
 
 ModelSpec ModelSpec::from_json(const Json &j) {
@@ -117,9 +133,14 @@ ModelSpec ModelSpec::from_json(const Json &j) {
         LayerSpec l;
         l.block = str_or(o, "block", "prenorm");
         l.mixer = PartSpec::from_json(o.get("mixer"));
-        l.feed_forward = PartSpec::from_json(o.get("feed_forward"));
+        l.feed_forward = part_or_none(o.get("feed_forward"));
         l.mixer_norm = PartSpec::from_json(o.get("mixer_norm"));
-        l.ffn_norm = PartSpec::from_json(o.get("ffn_norm"));
+        l.ffn_norm = part_or_none(o.get("ffn_norm"));
+        l.post_mixer_norm = part_or_none(o.get("post_mixer_norm"));
+        l.post_ffn_norm = part_or_none(o.get("post_ffn_norm"));
+        if (o.get("block_params").is_object()) l.block_params = o.get("block_params");
+        l.post_mixer_norm_name = str_or(o, "post_mixer_norm_name", l.post_mixer_norm_name);
+        l.post_ffn_norm_name = str_or(o, "post_ffn_norm_name", l.post_ffn_norm_name);
         l.prefix = str_or(o, "prefix", "");
         l.mixer_name = str_or(o, "mixer_name", l.mixer_name);
         l.ffn_name = str_or(o, "ffn_name", l.ffn_name);
@@ -135,6 +156,8 @@ ModelSpec ModelSpec::from_json(const Json &j) {
     }
     s.final_norm = PartSpec::from_json(j.get("final_norm"));
     s.tie_embeddings = j.get("tie_embeddings").as_bool();
+    s.position_table_name = str_or(j, "position_table_name", "");
+    if (j.get("logit_scale").is_number()) s.logit_scale = j.get("logit_scale").as_double();
     s.embedding_name = str_or(j, "embedding_name", s.embedding_name);
     s.final_norm_name = str_or(j, "final_norm_name", s.final_norm_name);
     s.head_name = str_or(j, "head_name", s.head_name);

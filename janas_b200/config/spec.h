@@ -48,14 +48,24 @@ struct PartSpec {
 // One layer: how its parts are arranged and where its tensors are found.
 // prefix is the layer's tensor-name prefix in the checkpoint; the four *_name
 // fields are the sub-prefixes of its parts below it.
+//
+// A part whose kind is empty is absent: a layer may have no feed-forward (then it
+// needs no ffn_norm either), and only some block arrangements have norms on the
+// sublayers' results (post_mixer_norm, post_ffn_norm).  block_params are the
+// arrangement's own constants and the names of tensors it owns (gates on the
+// residual branches, for instance); they are found below `prefix` too.
 struct LayerSpec {
     std::string block;
     PartSpec mixer, feed_forward, mixer_norm, ffn_norm;
+    PartSpec post_mixer_norm, post_ffn_norm;
+    Json block_params = Json::object();
     std::string prefix;
     std::string mixer_name = "self_attn";
     std::string ffn_name = "mlp";
     std::string mixer_norm_name = "input_layernorm";
     std::string ffn_norm_name = "post_attention_layernorm";
+    std::string post_mixer_norm_name = "post_mixer_norm";
+    std::string post_ffn_norm_name = "post_ffn_norm";
 };
 
 // One entry of the run order: run `layer` (its weights).  A layer may be named
@@ -74,6 +84,10 @@ struct ModelSpec {
     std::vector<RunEntry> run_order;
     PartSpec final_norm;
     bool tie_embeddings = false;
+    // a table [max_positions, hidden] of learned position vectors added to the
+    // embedding rows ("" for none), and a factor on the logits
+    std::string position_table_name;
+    double logit_scale = 1.0;
     std::string embedding_name = "model.embed_tokens.weight";
     std::string final_norm_name = "model.norm";
     std::string head_name = "lm_head.weight";

@@ -58,7 +58,17 @@ template <> __device__ __forceinline__ void load16<bf16>(const bf16 *p, float *o
     }
 }
 
-// Scratch per (row, head, chunk index): m, l, then hd weighted values.
+// Up to 16 values of a head whose size is no multiple of 16 (rows of such heads
+// lie at no 16-byte boundary): one by one, zeros beyond `count`.
+template <typename T> __device__ __forceinline__ void load_some(const T *p, float *out, int count)
+{
+#pragma unroll
+    for (int j = 0; j < 16; j++)
+        out[j] = j < count ? to_f(p[j]) : 0.0f;
+}
+
+// Scratch per (row, head, chunk index): m, l, then hd weighted values (hd: the
+// values' head size).
 __host__ __device__ inline size_t part_at(size_t row, int nh, int h, int max_chunks, int ci,
                                           int hd)
 {
@@ -72,7 +82,8 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
                     const T *__restrict__ v_cache, const int32_t *__restrict__ row_pos,
                     const int32_t *__restrict__ row_seq, const int32_t *__restrict__ block_table,
                     int bt_stride, float *__restrict__ part, int row0, int n_rows, int nh, int nkv,
-                    int hd, int window, float scale, int max_chunks)
+                    int hd, int vd, int window, float scale,
+                    const float *__restrict__ head_scale, int max_chunks)
 {
     constexpr int KPW = 32 / LPK;
     pdl_trigger();
@@ -97,7 +108,11 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
     int t0 = max(lo, c * ATT_CHUNK), t1 = min(pos, c * ATT_CHUNK + ATT_CHUNK - 1);
 
     int cidx = lane % LPK, ks = lane / LPK;
-    bool has_dims = cidx * 16 < hd;
+    // a lane's 16 values of the keys (and q) and of the values; heads that are no
+    // multiple of 16 are read value by value
+    bool has_dims = cidx * 16 < hd, has_vals = cidx * 16 < vd;
+    bool vec_k = hd % 16 == 0, vec_v = vd % 16 == 0;
+    int cnt_k = min(16, hd - cidx * 16), cnt_v = min(16, vd - cidx * 16);
     const int32_t *bt = block_table + (size_t)row_seq[row] * bt_stride;
 
     float qv[ATT_GT][16], o[ATT_GT][16], m[ATT_GT], l[ATT_GT];
@@ -108,9 +123,19 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
 #pragma unroll
         for (int j = 0; j < 16; j++)
             o[g][j] = qv[g][j] = 0.0f;
-        if (g < gt && has_dims)
-            load16<T>(q + ((size_t)row * nh + h0 + g) * hd + cidx * 16, qv[g]);
+        if (g < gt && has_dims) {
+            const T *qp = q + ((size_t)row * nh + h0 + g) * hd + cidx * 16;
+            if (vec_k)
+                load16<T>(qp, qv[g]);
+            else
+                load_some<T>(qp, qv[g], cnt_k);
+        }
     }
+    // a head's own factor on its scores (1 when the mixer has none)
+    float hs[ATT_GT];
+#pragma unroll
+    for (int g = 0; g < ATT_GT; g++)
+        hs[g] = head_scale != nullptr && g < gt ? head_scale[h0 + g] : 1.0f;
 
     for (int base = t0; base <= t1; base += KPW) {
         int t = base + ks;
@@ -122,9 +147,13 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
         size_t at = 0;
         if (valid) {
             int page = bt[t / PAGE];
-            at = (((size_t)page * nkv + kvh) * PAGE + (t % PAGE)) * hd + cidx * 16;
-            if (has_dims)
-                load16<T>(k_cache + at, kv);
+            at = ((size_t)page * nkv + kvh) * PAGE + (t % PAGE);
+            if (has_dims) {
+                if (vec_k)
+                    load16<T>(k_cache + at * hd + cidx * 16, kv);
+                else
+                    load_some<T>(k_cache + at * hd + cidx * 16, kv, cnt_k);
+            }
         }
         float s[ATT_GT];
 #pragma unroll
@@ -137,9 +166,19 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
             for (int off = 1; off < LPK; off <<= 1)
                 d += __shfl_xor_sync(0xffffffffu, d, off);
             s[g] = d * scale;
+            if (head_scale != nullptr)
+                s[g] *= hs[g];
         }
-        if (valid && has_dims)
-            load16<T>(v_cache + at, kv);
+        if (valid && has_vals) {
+            if (vec_v)
+                load16<T>(v_cache + at * vd + cidx * 16, kv);
+            else
+                load_some<T>(v_cache + at * vd + cidx * 16, kv, cnt_v);
+        } else if (valid) {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                kv[j] = 0.0f;
+        }
         if (valid) {
 #pragma unroll
             for (int g = 0; g < ATT_GT; g++) {
@@ -180,15 +219,16 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
         for (int g = 0; g < ATT_GT; g++) {
             if (g >= gt)
                 continue;
-            float *dst = part + part_at((size_t)lrow, nh, h0 + g, max_chunks, ci, hd);
+            float *dst = part + part_at((size_t)lrow, nh, h0 + g, max_chunks, ci, vd);
             if (lane == 0) {
                 dst[0] = m[g];
                 dst[1] = l[g];
             }
-            if (has_dims) {
+            if (has_vals) {
 #pragma unroll
                 for (int j = 0; j < 16; j++)
-                    dst[2 + cidx * 16 + j] = o[g][j];
+                    if (j < cnt_v)
+                        dst[2 + cidx * 16 + j] = o[g][j];
             }
         }
     }
@@ -231,7 +271,7 @@ template <typename T>
 __global__ void attn_merge_kernel(const float *__restrict__ part,
                                   const int32_t *__restrict__ row_pos, T *__restrict__ out,
                                   int row0, int nh, int hd, int window, int max_chunks,
-                                  int chunks_per_part)
+                                  int chunks_per_part, const float *__restrict__ sink)
 {
     pdl_trigger();
     pdl_wait();
@@ -254,6 +294,14 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
         for (int c0 = 0; c0 < n_chunks; c0 += 32)
             merge_partials<32>(base, stride, c0, n_chunks, d, hd, m, l, o);
     }
+    if (sink != nullptr) {
+        // a head's sink: one more term exp(sink) in the denominator, with no value
+        float sk = sink[h];
+        float mn = fmaxf(m, sk);
+        float a = expf(m - mn);
+        l = fmaf(l, a, expf(sk - mn));
+        o *= a;
+    }
     if (d < hd)
         out[((size_t)row * nh + h) * hd + d] = from_f<T>(o / l);
 }
@@ -262,17 +310,19 @@ template <typename T>
 static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const int32_t *row_pos,
                            const int32_t *row_seq, const int32_t *block_table, int bt_stride,
                            float *part, T *out, int row0, int n_rows, int nh, int nkv, int hd,
-                           int window, float scale, int max_chunks, cudaStream_t st)
+                           int vd, int window, float scale, const float *head_scale,
+                           const float *sink, int max_chunks, cudaStream_t st)
 {
     int lpk = 1;
-    while (lpk * 16 < hd)
+    while (lpk * 16 < max(hd, vd))
         lpk <<= 1;
     int group = nh / nkv;
     size_t items = (size_t)n_rows * max_chunks;
     dim3 grid((unsigned)((items + 3) / 4), nkv, (group + ATT_GT - 1) / ATT_GT);
 #define JB_ATT(L)                                                                            \
     launch(attn_partial_kernel<T, L>, grid, 128, 0, st, q, k_cache, v_cache, row_pos, row_seq, \
-           block_table, bt_stride, part, row0, n_rows, nh, nkv, hd, window, scale, max_chunks)
+           block_table, bt_stride, part, row0, n_rows, nh, nkv, hd, vd, window, scale,        \
+           head_scale, max_chunks)
     switch (lpk) {
     case 1: JB_ATT(1); break;
     case 2: JB_ATT(2); break;
@@ -285,8 +335,8 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
 #undef JB_ATT
     if (cudaGetLastError() != cudaSuccess)
         return JB_ELAUNCH;
-    launch(attn_merge_kernel<T>, dim3(n_rows, nh), (hd + 31) / 32 * 32, 0, st, (const float *)part,
-           row_pos, out, row0, nh, hd, window, max_chunks, 1);
+    launch(attn_merge_kernel<T>, dim3(n_rows, nh), (vd + 31) / 32 * 32, 0, st, (const float *)part,
+           row_pos, out, row0, nh, vd, window, max_chunks, 1, sink);
     return launch_status();
 }
 
@@ -311,21 +361,40 @@ extern "C" int jb_attention(const void *q, const void *k_cache, const void *v_ca
                             int row0, int n_rows, int nh, int nkv, int hd, int window, float scale,
                             int max_chunks, cudaStream_t st)
 {
+    if (hd % 16)
+        return JB_EINVAL;
+    return jb_attention_sink(q, k_cache, v_cache, dt, row_pos, row_seq, block_table, bt_stride,
+                             scratch, out, row0, n_rows, nh, nkv, hd, hd, window, scale, nullptr,
+                             nullptr, max_chunks, st);
+}
+
+// The same with what some mixers add: values of another head size than the keys
+// (vd; out is then [n, nh, vd] and the scratch is counted with vd), a factor per
+// head on the scores (head_scale, float [nh], or null) and a sink per head (sink,
+// float [nh], or null): exp(sink) joins the softmax's denominator once, with no
+// key and no value.  Head sizes that are no multiple of 16 are read value by value.
+extern "C" int jb_attention_sink(const void *q, const void *k_cache, const void *v_cache, int dt,
+                                 const int32_t *row_pos, const int32_t *row_seq,
+                                 const int32_t *block_table, int bt_stride, float *scratch,
+                                 void *out, int row0, int n_rows, int nh, int nkv, int hd, int vd,
+                                 int window, float scale, const float *head_scale,
+                                 const float *sink, int max_chunks, cudaStream_t st)
+{
     if (n_rows <= 0)
         return JB_OK;
-    if (hd % 16 || hd > 512 || hd <= 0 || nkv <= 0 || nh % nkv || max_chunks <= 0 ||
+    if (hd > 512 || hd <= 0 || vd > 512 || vd <= 0 || nkv <= 0 || nh % nkv || max_chunks <= 0 ||
         nkv > 65535 || nh > 65535)
         return JB_EINVAL;
     if (dt == JB_F32)
         return attention_typed<float>((const float *)q, (const float *)k_cache,
                                       (const float *)v_cache, row_pos, row_seq, block_table,
                                       bt_stride, scratch, (float *)out, row0, n_rows, nh, nkv, hd,
-                                      window, scale, max_chunks, st);
+                                      vd, window, scale, head_scale, sink, max_chunks, st);
     if (dt == JB_BF16)
         return attention_typed<bf16>((const bf16 *)q, (const bf16 *)k_cache,
                                      (const bf16 *)v_cache, row_pos, row_seq, block_table,
                                      bt_stride, scratch, (bf16 *)out, row0, n_rows, nh, nkv, hd,
-                                     window, scale, max_chunks, st);
+                                     vd, window, scale, head_scale, sink, max_chunks, st);
     return JB_EINVAL;
 }
 
@@ -337,6 +406,16 @@ extern "C" int jb_attention_merge(const float *scratch, const int32_t *row_pos, 
                                   int row0, int n_rows, int nh, int hd, int window, int max_parts,
                                   int chunks_per_part, cudaStream_t st)
 {
+    return jb_attention_merge_sink(scratch, row_pos, out, dt, row0, n_rows, nh, hd, window,
+                                   max_parts, chunks_per_part, nullptr, st);
+}
+
+// The same with a sink per head (float [nh], or null) joining the denominator.
+extern "C" int jb_attention_merge_sink(const float *scratch, const int32_t *row_pos, void *out,
+                                       int dt, int row0, int n_rows, int nh, int hd, int window,
+                                       int max_parts, int chunks_per_part, const float *sink,
+                                       cudaStream_t st)
+{
     if (n_rows <= 0)
         return JB_OK;
     if (hd <= 0 || hd > 512 || nh <= 0 || nh > 65535 || max_parts <= 0 || chunks_per_part <= 0)
@@ -345,10 +424,10 @@ extern "C" int jb_attention_merge(const float *scratch, const int32_t *row_pos, 
     int threads = (hd + 31) / 32 * 32;
     if (dt == JB_F32)
         launch(attn_merge_kernel<float>, grid, threads, 0, st, scratch, row_pos, (float *)out, row0,
-               nh, hd, window, max_parts, chunks_per_part);
+               nh, hd, window, max_parts, chunks_per_part, sink);
     else if (dt == JB_BF16)
         launch(attn_merge_kernel<bf16>, grid, threads, 0, st, scratch, row_pos, (bf16 *)out, row0,
-               nh, hd, window, max_parts, chunks_per_part);
+               nh, hd, window, max_parts, chunks_per_part, sink);
     else
         return JB_EINVAL;
     return launch_status();

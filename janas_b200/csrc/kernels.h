@@ -49,6 +49,37 @@ int jb_attention(const void *q, const void *k_cache, const void *v_cache, int dt
 int jb_attention_merge(const float *scratch, const int32_t *row_pos, void *out, int dt, int row0,
                        int n_rows, int nh, int hd, int window, int max_parts, int chunks_per_part,
                        cudaStream_t st);
+int jb_attention_sink(const void *q, const void *k_cache, const void *v_cache, int dt,
+                      const int32_t *row_pos, const int32_t *row_seq, const int32_t *block_table,
+                      int bt_stride, float *scratch, void *out, int row0, int n_rows, int nh,
+                      int nkv, int hd, int vd, int window, float scale, const float *head_scale,
+                      const float *sink, int max_chunks, cudaStream_t st);
+int jb_attention_merge_sink(const float *scratch, const int32_t *row_pos, void *out, int dt,
+                            int row0, int n_rows, int nh, int hd, int window, int max_parts,
+                            int chunks_per_part, const float *sink, cudaStream_t st);
+int jb_embed_pos(const void *table, int table_dt, const void *pos_table, int pos_dt,
+                 const int32_t *tokens, const int32_t *row_pos, float *x, int n, int dm,
+                 cudaStream_t st);
+int jb_dyt(float *x, const float *delta, int S, long long delta_stride, const int32_t *row_idx,
+           const float *w, const float *b, const float *alpha, void *out, int out_dt, int n_out,
+           int dm, cudaStream_t st);
+int jb_gate_mul(const float *y, int Sy, long long y_stride, const float *y_bias, const float *g,
+                int Sg, long long g_stride, int g_ld, int g_col0, const float *g_bias, float *out,
+                int n, int dm, cudaStream_t st);
+int jb_gated_dyt_residual(float *x, const float *y, int Sy, long long y_stride,
+                          const float *y_bias, const float *g, int Sg, long long g_stride,
+                          int g_ld, int g_col0, const float *g_bias, const float *pw,
+                          const float *pb, const float *palpha, const float *nw, const float *nb,
+                          const float *nalpha, void *out, int out_dt, int n, int dm,
+                          cudaStream_t st);
+int jb_polynorm(const float *z, int S, long long stride, int z_ld, const float *coef, float eps,
+                void *out, int out_dt, int n, int ff, cudaStream_t st);
+int jb_scale(float *x, float s, long long total, cudaStream_t st);
+int jb_add_bias(float *y, const float *bias, int n, int m, cudaStream_t st);
+int jb_qkv_bias_append(const float *qkv, int S, long long stride, int ld, const float *bias,
+                       const int32_t *row_pos, const int32_t *row_seq, const int32_t *block_table,
+                       int bt_stride, void *q_out, void *k_cache, void *v_cache, int cache_dt,
+                       int n, int nh, int nkv, int hd, int vd, int append, cudaStream_t st);
 int jb_attn_tc_decode_runs(int nh, int nkv, int hd);
 int jb_attn_tc_ok(int nh, int nkv, int hd);
 int jb_attn_tc_block_positions(int nh, int nkv);

@@ -40,13 +40,99 @@ int sample_small_cap() { return jb_sample_small_cap(); }
 bool sample_needs_big(int vocab, int top_k) { return jb_sample_needs_big(vocab, top_k) != 0; }
 
 // ------------------------------------------------------------------ row-wise
-Buf embed(Device &d, const DevTensor &table, const int32_t *tokens, long long n) {
+Buf embed(Device &d, const DevTensor &table, const int32_t *tokens, long long n, const DevTensor *pos_table,
+          const int32_t *row_pos) {
     need_float(table.dt, "embedding table");
     long long dm = table.shape.at(1);
     Buf x = d.pool.get((size_t)n * (size_t)dm * 4);
+    if (pos_table) {
+        need_float(pos_table->dt, "position table");
+        if (pos_table->shape.size() != 2 || pos_table->shape[1] != dm || !row_pos)
+            fail(JB_LLM_EINVAL, "embed: the position table's rows are not as wide as the embedding's");
+        check(jb_embed_pos(table.ptr, table.dt, pos_table->ptr, pos_table->dt, tokens, row_pos, x.as<float>(),
+                           as_int(n, "rows"), as_int(dm, "width"), d.stream), "embed");
+        return x;
+    }
     check(jb_embed(table.ptr, table.dt, tokens, x.as<float>(), as_int(n, "rows"), as_int(dm, "width"),
                    d.stream), "embed");
     return x;
+}
+
+Buf dyt(Device &d, float *x, long long n, long long dm, const DytParams &p, DType out_dt, const Stack *delta,
+        const int32_t *rows, long long n_out) {
+    need_float(out_dt, "norm output");
+    if (delta && rows) {
+        add_(d, x, n, dm, *delta);
+        delta = nullptr;
+    }
+    if (delta && (delta->n != n || delta->m != dm)) fail(JB_LLM_EINVAL, "dyt: delta's shape is not x's");
+    if (delta) resolve_bias(d, const_cast<Stack &>(*delta));
+    long long outs = rows ? n_out : n;
+    Buf out = d.pool.get((size_t)outs * (size_t)dm * dtype_size(out_dt));
+    check(jb_dyt(x, delta ? delta->data() : nullptr, delta ? delta->S : 0, delta ? delta->stride() : 0, rows,
+                 p.w, p.b, p.alpha, out.ptr, out_dt, as_int(outs, "rows"), as_int(dm, "width"), d.stream),
+          "dyt");
+    return out;
+}
+
+static void gate_shapes(const Stack &y, const Stack &g, long long g_col0, const char *what) {
+    if (g.n != y.n || g_col0 < 0 || g_col0 + y.m > g.m)
+        fail(JB_LLM_EINVAL, std::string(what) + ": the gate does not cover the sublayer's result");
+}
+
+Buf gate_mul(Device &d, const Stack &y, const Stack &g, long long g_col0, const float *g_bias) {
+    const float *y_bias = y.bias;
+    gate_shapes(y, g, g_col0, "gate_mul");
+    Buf out = d.pool.get((size_t)y.n * (size_t)y.m * 4);
+    check(jb_gate_mul(y.data(), y.S, y.stride(), y_bias, g.data(), g.S, g.stride(), as_int(g.m, "width"),
+                      (int)g_col0, g_bias, out.as<float>(), as_int(y.n, "rows"), as_int(y.m, "width"),
+                      d.stream), "gate_mul");
+    return out;
+}
+
+Buf gated_dyt_residual(Device &d, float *x, const Stack &y, const Stack &g, long long g_col0,
+                       const float *g_bias, const DytParams &post, const DytParams *next, DType out_dt) {
+    const float *y_bias = y.bias;
+    gate_shapes(y, g, g_col0, "gated_dyt_residual");
+    Buf out;
+    if (next) {
+        need_float(out_dt, "norm output");
+        out = d.pool.get((size_t)y.n * (size_t)y.m * dtype_size(out_dt));
+    }
+    check(jb_gated_dyt_residual(x, y.data(), y.S, y.stride(), y_bias, g.data(), g.S, g.stride(),
+                                as_int(g.m, "width"), (int)g_col0, g_bias, post.w, post.b, post.alpha,
+                                next ? next->w : nullptr, next ? next->b : nullptr,
+                                next ? next->alpha : nullptr, out.ptr, out_dt, as_int(y.n, "rows"),
+                                as_int(y.m, "width"), d.stream), "gated_dyt_residual");
+    return out;
+}
+
+Buf polynorm(Device &d, const Stack &z, long long ff, const float *coef, float eps, DType out_dt) {
+    need_float(out_dt, "activation output");
+    if (ff <= 0 || ff > z.m) fail(JB_LLM_EINVAL, "polynorm: the product is narrower than the feed-forward");
+    Buf out = d.pool.get((size_t)z.n * (size_t)ff * dtype_size(out_dt));
+    check(jb_polynorm(z.data(), z.S, z.stride(), as_int(z.m, "width"), coef, eps, out.ptr, out_dt,
+                      as_int(z.n, "rows"), as_int(ff, "width"), d.stream), "polynorm");
+    return out;
+}
+
+void scale_(Device &d, float *x, long long total, float s) {
+    check(jb_scale(x, s, total, d.stream), "scale");
+}
+
+Buf qkv_bias_append(Device &d, const Stack &qkv, const float *bias, const int32_t *row_pos,
+                    const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt,
+                    bool append) {
+    long long width = (long long)g.nh * g.hd + (append ? (long long)g.nkv * (g.hd + g.value_dim()) : 0);
+    if (qkv.m < width) fail(JB_LLM_EINVAL, "qkv_bias_append: the product is narrower than q, k and v");
+    if (append && (!c.k || !c.v)) fail(JB_LLM_EINVAL, "qkv_bias_append: no cache to append to");
+    if (append && c.dt != out_dt) fail(JB_LLM_EINVAL, "qkv_bias_append: the cache is of another type");
+    Buf q = d.pool.get((size_t)qkv.n * (size_t)g.nh * (size_t)g.hd * dtype_size(out_dt));
+    check(jb_qkv_bias_append(qkv.data(), qkv.S, qkv.stride(), as_int(qkv.m, "width"), bias, row_pos, row_seq,
+                             c.block_table, c.bt_stride, q.ptr, append ? c.k : nullptr, append ? c.v : nullptr,
+                             out_dt, as_int(qkv.n, "rows"), g.nh, g.nkv, g.hd, g.value_dim(), append ? 1 : 0,
+                             d.stream), "qkv_bias_append");
+    return q;
 }
 
 Buf rmsnorm(Device &d, float *x, long long n, long long dm, const DevTensor &w, float eps, DType out_dt,
@@ -54,6 +140,7 @@ Buf rmsnorm(Device &d, float *x, long long n, long long dm, const DevTensor &w, 
     need_float(w.dt, "norm weight");
     need_float(out_dt, "norm output");
     if (w.numel() != dm) fail(JB_LLM_EINVAL, "rmsnorm: the weight's length is not the rows' width");
+    if (delta) resolve_bias(d, const_cast<Stack &>(*delta));
     if (delta && rows) {
         add_(d, x, n, dm, *delta);
         delta = nullptr;
@@ -68,8 +155,19 @@ Buf rmsnorm(Device &d, float *x, long long n, long long dm, const DevTensor &w, 
     return out;
 }
 
+void add_bias_(Device &d, float *y, long long n, long long m, const float *bias) {
+    check(jb_add_bias(y, bias, as_int(n, "rows"), as_int(m, "width"), d.stream), "add_bias");
+}
+
+void resolve_bias(Device &d, Stack &y) {
+    if (!y.bias || !y) return;
+    add_bias_(d, y.data(), y.n, y.m, y.bias);
+    y.bias = nullptr;
+}
+
 void add_(Device &d, float *x, long long n, long long dm, const Stack &delta) {
     if (delta.n != n || delta.m != dm) fail(JB_LLM_EINVAL, "add: delta's shape is not x's");
+    resolve_bias(d, const_cast<Stack &>(delta));
     check(jb_rmsnorm(x, delta.data(), delta.S, delta.stride(), nullptr, nullptr, 0, nullptr, 0,
                      as_int(n, "rows"), as_int(dm, "width"), 0.0f, d.stream), "add");
 }
@@ -199,8 +297,10 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
               int n_blocks, bool decode, bool force_simt) {
     need_float(c.dt, "attention");
     int ni = as_int(n, "rows");
-    Buf out = d.pool.get((size_t)n * (size_t)g.nh * (size_t)g.hd * dtype_size(c.dt));
-    bool tc = !force_simt && c.dt == BF16 && (decode || blocks != nullptr) && attention_tc_ok(g.nh, g.nkv, g.hd);
+    int vd = g.value_dim();
+    Buf out = d.pool.get((size_t)n * (size_t)g.nh * (size_t)vd * dtype_size(c.dt));
+    bool tc = !force_simt && g.plain() && c.dt == BF16 && (decode || blocks != nullptr) &&
+              attention_tc_ok(g.nh, g.nkv, g.hd);
     if (tc && !decode) {
         check(jb_attn_tc_prefill(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
                                  out.ptr, ni, g.nh, g.nkv, g.hd, g.window, g.scale, d.stream),
@@ -215,7 +315,7 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
         per_cta = (max_chunks + parts - 1) / parts;
         parts = (max_chunks + per_cta - 1) / per_cta;
     }
-    long long per_row = jb_attention_scratch(1, g.nh, g.hd, parts);
+    long long per_row = jb_attention_scratch(1, g.nh, vd, parts);
     long long rows_per_call = std::max<long long>(1, std::min<long long>(n, (long long)(ATT_SCRATCH_BYTES / 4) /
                                                                                  std::max<long long>(per_row, 1)));
     Buf scratch = d.pool.get((size_t)per_row * (size_t)rows_per_call * 4);
@@ -228,9 +328,10 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
             check(jb_attention_merge(scratch.as<float>(), row_pos, out.ptr, c.dt, (int)row0, cnt, g.nh, g.hd,
                                      g.window, parts, per_cta, d.stream), "attention merge");
         } else {
-            check(jb_attention(q, c.k, c.v, c.dt, row_pos, row_seq, c.block_table, c.bt_stride,
-                               scratch.as<float>(), out.ptr, (int)row0, cnt, g.nh, g.nkv, g.hd, g.window,
-                               g.scale, max_chunks, d.stream), "attention", 2);
+            check(jb_attention_sink(q, c.k, c.v, c.dt, row_pos, row_seq, c.block_table, c.bt_stride,
+                                    scratch.as<float>(), out.ptr, (int)row0, cnt, g.nh, g.nkv, g.hd, vd,
+                                    g.window, g.scale, g.head_scale, g.sink, max_chunks, d.stream),
+                  "attention", 2);
         }
     }
     return out;

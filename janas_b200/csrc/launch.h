@@ -23,6 +23,10 @@ struct Stack {
     Buf buf;
     int S = 0;
     long long n = 0, m = 0;
+    // float32 [m] on the device, still to be added once to every row of the sum (a
+    // product's bias), or null.  The kernels that end a sublayer take it as it is;
+    // for every other consumer resolve_bias() adds it into the first partial sum.
+    const float *bias = nullptr;
     float *data() const { return (float *)buf.ptr; }
     long long stride() const { return n * m; }
     explicit operator bool() const { return S > 0; }
@@ -38,8 +42,30 @@ int attention_chunk();
 int sample_small_cap();
 bool sample_needs_big(int vocab, int top_k);
 
-// x[j, :] = table[tokens[j], :] as float32 [n, dm]
-Buf embed(Device &d, const DevTensor &table, const int32_t *tokens, long long n);
+// x[j, :] = table[tokens[j], :] as float32 [n, dm]; with a table of learned
+// position vectors, plus pos_table[row_pos[j], :]
+Buf embed(Device &d, const DevTensor &table, const int32_t *tokens, long long n,
+          const DevTensor *pos_table = nullptr, const int32_t *row_pos = nullptr);
+
+// The Dynamic Tanh norm's parameters on the device, all float32: w and b [dm], alpha [1].
+struct DytParams {
+    const float *w = nullptr, *b = nullptr, *alpha = nullptr;
+};
+// tanh(alpha x) w + b on the rows of x (float32 [n, dm]); delta and rows as in rmsnorm.
+Buf dyt(Device &d, float *x, long long n, long long dm, const DytParams &p, DType out_dt,
+        const Stack *delta, const int32_t *rows, long long n_out);
+// (sum y + y.bias) * sigmoid(sum g + g_bias) as float32 [n, dm].  g's rows may be wider
+// than dm: the gate is then its columns g_col0 .. g_col0 + dm - 1.  Biases: float32 [dm] or null.
+Buf gate_mul(Device &d, const Stack &y, const Stack &g, long long g_col0, const float *g_bias);
+// adds y.bias into y's first partial sum and clears it (nothing when there is none)
+void resolve_bias(Device &d, Stack &y);
+// x += dyt_post(gate_mul(...)) in place; with `next`, also returns dyt_next(x) in out_dt.
+Buf gated_dyt_residual(Device &d, float *x, const Stack &y, const Stack &g, long long g_col0,
+                       const float *g_bias, const DytParams &post, const DytParams *next, DType out_dt);
+// c0 n(z) + c1 n(z^2) + c2 n(z^3) + c3 over the first ff columns of z's rows,
+// n(u) = u / sqrt(mean(u^2) + eps); coef: float32 [4] on the device.  [n, ff] in out_dt.
+Buf polynorm(Device &d, const Stack &z, long long ff, const float *coef, float eps, DType out_dt);
+void scale_(Device &d, float *x, long long total, float s);
 
 // RMSNorm of the rows of x (float32 [n, dm]).  With delta, x is first updated in
 // place, x += delta[0] + ... + delta[S-1].  With rows (n_out int32 indices on the
@@ -48,6 +74,8 @@ Buf embed(Device &d, const DevTensor &table, const int32_t *tokens, long long n)
 Buf rmsnorm(Device &d, float *x, long long n, long long dm, const DevTensor &weight, float eps,
             DType out_dt, const Stack *delta, const int32_t *rows, long long n_out);
 void add_(Device &d, float *x, long long n, long long dm, const Stack &delta);
+// y[r, :] += bias for every row of y (float32 [n, m])
+void add_bias_(Device &d, float *y, long long n, long long m, const float *bias);
 
 // SiLU(gate) * up for a stack [S, n, 2 ff] whose columns are [gate | up]
 Buf swiglu(Device &d, const Stack &gate_up, DType out_dt);
@@ -72,6 +100,11 @@ Buf linear_swiglu(Device &d, const void *a, DType a_dt, long long n, long long k
 struct AttnGeometry {
     int nh = 0, nkv = 0, hd = 0, window = 0;
     float scale = 1.0f;
+    int vd = 0;                              // the values' head size; 0: as the keys'
+    const float *head_scale = nullptr;       // float32 [nh] on the device: a factor per head on the scores
+    const float *sink = nullptr;             // float32 [nh]: exp(sink) joins each softmax's denominator
+    int value_dim() const { return vd > 0 ? vd : hd; }
+    bool plain() const { return !head_scale && !sink && value_dim() == hd; }
 };
 
 // what the attention kernels see of the cache and of the step's index arrays
@@ -92,6 +125,14 @@ Buf qk_norm_rope_append(Device &d, const Stack &qkv, const DevTensor *q_w, const
                         float eps, const float *cos, const float *sin, const int32_t *row_pos,
                         const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g,
                         DType out_dt);
+
+// The fused [q | k | v] product's sums plus a bias (float32 over the product's
+// columns, or null): q [n, heads, hd] in out_dt comes back, K and V go to the
+// cache pages at the rows' positions.  With append false the product holds q alone
+// (a mixer that reads another's keys and values).
+Buf qkv_bias_append(Device &d, const Stack &qkv, const float *bias, const int32_t *row_pos,
+                    const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt,
+                    bool append);
 
 // The blocks a prefill step is cut into for the tensor-core kernel: int32
 // [blocks, 4] = first row, positions, the first row's position, sequence;

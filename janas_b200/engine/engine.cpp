@@ -168,6 +168,7 @@ std::vector<LayerCache> Engine::layer_caches(
             lc.kv.bt_stride = it->second.second;
             lc.kv_heads = g->spec.num_kv_heads;
             lc.head_dim = g->spec.head_dim;
+            lc.v_head_dim = g->spec.value_dim();
         }
         out.push_back(lc);
     }

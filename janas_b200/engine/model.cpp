@@ -7,38 +7,43 @@ namespace jb {
 DecoderModel::DecoderModel(const ModelSpec &s, DType dt, Device *d) : spec(s), dtype(dt), dev(d) {
     spec.validate();
     if (dt != F32 && dt != BF16) fail(JB_LLM_EINVAL, "the compute dtype is float32 or bfloat16");
-    for (auto &ls : spec.layers)
-        blocks.push_back(build_block(ls.block, build_mixer(ls.mixer, dt, d),
-                                     build_feed_forward(ls.feed_forward, dt, d),
-                                     build_norm(ls.mixer_norm, dt, d), build_norm(ls.ffn_norm, dt, d)));
+    for (auto &ls : spec.layers) blocks.push_back(build_block(ls, dt, d));
     final_norm = build_norm(spec.final_norm, dt, d);
     if (final_norm->size() != spec.hidden_size)
         config_error("the final norm's size is not the model's hidden size");
 }
 
-void DecoderModel::layer_names(int i, std::string n[4]) const {
+void DecoderModel::layer_names(int i, std::string n[6]) const {
     const LayerSpec &ls = spec.layers[(size_t)i];
     n[0] = Part::name(ls.prefix, ls.mixer_name);
     n[1] = Part::name(ls.prefix, ls.ffn_name);
     n[2] = Part::name(ls.prefix, ls.mixer_norm_name);
     n[3] = Part::name(ls.prefix, ls.ffn_norm_name);
+    n[4] = Part::name(ls.prefix, ls.post_mixer_norm_name);
+    n[5] = Part::name(ls.prefix, ls.post_ffn_norm_name);
 }
 
 TensorList DecoderModel::layer_tensors(int i) const {
-    std::string n[4];
+    std::string n[6];
     layer_names(i, n);
     TensorList t;
     const Block &b = *blocks[(size_t)i];
     b.mixer_norm->tensors(n[2], t);
     b.mixer->tensors(n[0], t);
-    b.ffn_norm->tensors(n[3], t);
-    b.feed_forward->tensors(n[1], t);
+    if (b.post_mixer_norm) b.post_mixer_norm->tensors(n[4], t);
+    if (b.ffn_norm) b.ffn_norm->tensors(n[3], t);
+    if (b.feed_forward) b.feed_forward->tensors(n[1], t);
+    if (b.post_ffn_norm) b.post_ffn_norm->tensors(n[5], t);
+    b.tensors(spec.layers[(size_t)i].prefix, t);
     return t;
 }
 
 TensorList DecoderModel::top_tensors() const {
     TensorList t;
     t.emplace_back(spec.embedding_name, TensorSpec{{spec.vocab_size, spec.hidden_size}, EMBEDDING, false});
+    if (!spec.position_table_name.empty())
+        t.emplace_back(spec.position_table_name,
+                       TensorSpec{{spec.max_positions, spec.hidden_size}, EMBEDDING, false});
     final_norm->tensors(spec.final_norm_name, t);
     t.emplace_back(spec.head_name, TensorSpec{{spec.vocab_size, spec.hidden_size}, MATRIX, spec.tie_embeddings});
     return t;
@@ -47,12 +52,13 @@ TensorList DecoderModel::top_tensors() const {
 TensorList DecoderModel::tensors() const {
     TensorList top = top_tensors();
     TensorList t;
-    t.push_back(top.front());
+    size_t first = spec.position_table_name.empty() ? 1 : 2;     // the tables come first
+    t.insert(t.end(), top.begin(), top.begin() + first);
     for (size_t i = 0; i < blocks.size(); i++) {
         TensorList l = layer_tensors((int)i);
         t.insert(t.end(), l.begin(), l.end());
     }
-    t.insert(t.end(), top.begin() + 1, top.end());
+    t.insert(t.end(), top.begin() + first, top.end());
     std::set<std::string> seen;
     for (auto &kv : t)
         if (!seen.insert(kv.first).second) config_error("two parts of the model name the tensor " + kv.first);
@@ -61,6 +67,7 @@ TensorList DecoderModel::tensors() const {
 
 void DecoderModel::load_top(TensorMap &t) {
     embedding = Part::take(t, spec.embedding_name);
+    if (!spec.position_table_name.empty()) position_table = Part::take(t, spec.position_table_name);
     auto it = t.find(spec.head_name);
     if (it != t.end()) {
         head = it->second;
@@ -74,13 +81,16 @@ void DecoderModel::load_top(TensorMap &t) {
 }
 
 void DecoderModel::load_layer(int i, TensorMap &t) {
-    std::string n[4];
+    std::string n[6];
     layer_names(i, n);
     Block &b = *blocks[(size_t)i];
     b.mixer_norm->load(n[2], t);
     b.mixer->load(n[0], t);
-    b.ffn_norm->load(n[3], t);
-    b.feed_forward->load(n[1], t);
+    if (b.post_mixer_norm) b.post_mixer_norm->load(n[4], t);
+    if (b.ffn_norm) b.ffn_norm->load(n[3], t);
+    if (b.feed_forward) b.feed_forward->load(n[1], t);
+    if (b.post_ffn_norm) b.post_ffn_norm->load(n[5], t);
+    b.load(spec.layers[(size_t)i].prefix, t);
 }
 
 void DecoderModel::load_checkpoint(const Checkpoint &ckpt) {
@@ -132,8 +142,10 @@ size_t DecoderModel::weight_bytes() const {
     for (auto &e : spec.run_order) used.insert(e.layer);
     for (int layer : used) {
         const Block &b = *blocks[(size_t)layer];
-        total += b.mixer->weight_bytes() + b.feed_forward->weight_bytes() + b.mixer_norm->weight_bytes() +
-                 b.ffn_norm->weight_bytes();
+        total += b.mixer->weight_bytes() + b.mixer_norm->weight_bytes() + b.weight_bytes();
+        for (const Part *p : {(const Part *)b.feed_forward.get(), (const Part *)b.ffn_norm.get(),
+                              (const Part *)b.post_mixer_norm.get(), (const Part *)b.post_ffn_norm.get()})
+            if (p) total += p->weight_bytes();
     }
     return total + final_norm->weight_bytes();
 }
@@ -163,7 +175,7 @@ bool DecoderModel::supports(StepKind kind) const {
 
 bool DecoderModel::graph_safe() const {
     for (auto &b : blocks)
-        if (!b->mixer->graph_safe() || !b->feed_forward->graph_safe()) return false;
+        if (!b->mixer->graph_safe() || (b->feed_forward && !b->feed_forward->graph_safe())) return false;
     return true;
 }
 
@@ -172,10 +184,20 @@ Buf DecoderModel::forward(StepContext &ctx, const int32_t *tokens, std::vector<L
     if (!loaded) fail(JB_LLM_EFAIL, "the model has no weights yet");
     Device &d = *ctx.dev;
     long long n = ctx.n_rows;
-    Buf x = ops::embed(d, embedding, tokens, n);
+    if (position_table && ctx.max_pos >= position_table.shape.at(0))
+        fail(JB_LLM_EINVAL, fmt("position %lld is beyond the %lld learned position vectors", ctx.max_pos,
+                                position_table.shape.at(0)));
+    Buf x = ops::embed(d, embedding, tokens, n, position_table ? &position_table : nullptr, ctx.row_pos);
     Stack pending;
+    ctx.normed.reset();
+    ctx.normed_by = nullptr;
     for (size_t e = 0; e < spec.run_order.size(); e++) {
-        blocks[(size_t)spec.run_order[e].layer]->forward(ctx, x.as<float>(), pending, caches[e]);
+        Block &b = *blocks[(size_t)spec.run_order[e].layer];
+        // the norm that meets the residual stream next: the next entry's first one (the
+        // model's last norm runs on the wanted rows alone and is not computed ahead)
+        b.next_norm = e + 1 < spec.run_order.size()
+                          ? blocks[(size_t)spec.run_order[e + 1].layer]->mixer_norm.get() : nullptr;
+        b.forward(ctx, x.as<float>(), pending, caches[e]);
         if (ctx.trace) {
             if (pending) {
                 ops::add_(d, x.as<float>(), n, spec.hidden_size, pending);
@@ -193,6 +215,8 @@ Buf DecoderModel::forward(StepContext &ctx, const int32_t *tokens, std::vector<L
     Buf h = final_norm->apply(ctx, x.as<float>(), n, ctx.dtype, pending ? &pending : nullptr,
                               all ? nullptr : want_rows, all ? 0 : n_want);
     Stack lg = ops::linear(d, h.ptr, ctx.dtype, all ? n : n_want, spec.hidden_size, head, true);
+    if (spec.logit_scale != 1.0)
+        ops::scale_(d, lg.data(), (all ? n : n_want) * spec.vocab_size, (float)spec.logit_scale);
     return std::move(lg.buf);
 }
 

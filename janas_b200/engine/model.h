@@ -62,11 +62,11 @@ public:
     Device *dev;
     std::vector<std::unique_ptr<Block>> blocks;
     std::unique_ptr<Norm> final_norm;
-    DevTensor embedding, head;
+    DevTensor embedding, head, position_table;
     bool loaded = false;
 
 private:
-    void layer_names(int i, std::string n[4]) const;
+    void layer_names(int i, std::string n[6]) const;
 };
 
 }  // namespace jb

@@ -165,9 +165,173 @@ private:
     int chunk_ = 0;
 };
 
+// Grouped-query attention without a rotation, with what some designs add to it:
+// biases on the four products, a scale given as a constant, a learned factor per
+// head on the scores, a learned sink per head in the softmax's denominator, values
+// of another head size than the keys, and keys and values taken from another
+// layer's cache.
+//
+//   q = Wq h + bq, k = Wk h + bk, v = Wv h + bv            (k, v only with own_kv)
+//   s_ij = (q_i . k_j) * scale * temp_a,  j <= i  (and within the window, if any)
+//   p_ij = exp(s_ij) / (exp(sink_a) + sum_j exp(s_ij));   out = Wo concat(p v) + bo
+//
+// params: hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim (default: head_dim),
+// scale (default 1/sqrt(head_dim)), window (0: none), bias, head_scale, sink, own_kv
+// (booleans; own_kv false: the run order gives this layer another entry's cache and it
+// has no key and value products), names (optional): q, k, v, o, bias (a suffix),
+// head_scale, sink.
+class SinkAttention : public Mixer {
+public:
+    SinkAttention(const PartSpec &s, DType dt, Device *d) : Mixer(s, dt, d) {
+        hidden_ = s.get_int("hidden_size");
+        g_.nh = (int)s.get_int("num_heads");
+        g_.nkv = (int)s.get_int("num_kv_heads");
+        g_.hd = (int)s.get_int("head_dim");
+        g_.vd = (int)s.get_int("v_head_dim", g_.hd);
+        g_.window = (int)s.get_int("window", 0);
+        g_.scale = s.has("scale") ? (float)s.get_double("scale") : (float)(1.0 / std::sqrt((double)g_.hd));
+        bias_ = flag(s, "bias", false);
+        head_scale_ = flag(s, "head_scale", false);
+        sink_ = flag(s, "sink", false);
+        own_kv_ = flag(s, "own_kv", true);
+        if (hidden_ <= 0 || g_.nh <= 0 || g_.nkv <= 0) config_error("sink_attention: sizes must be positive");
+        if (g_.nh % g_.nkv) config_error("sink_attention: num_heads must be a multiple of num_kv_heads");
+        if (g_.hd <= 0 || g_.hd > 512 || g_.vd <= 0 || g_.vd > 512)
+            config_error(fmt("sink_attention: head sizes %d and %d: the kernels take 1 to 512", g_.hd, g_.vd));
+        if (g_.window < 0) config_error("sink_attention: window must not be negative");
+        const Json &nm = s.params.get("names");
+        auto leaf = [&](const char *key, const char *dflt) {
+            return nm.is_object() && nm.get(key).is_string() ? nm.get(key).as_string() : std::string(dflt);
+        };
+        n_q_ = leaf("q", "q_proj.weight");
+        n_k_ = leaf("k", "k_proj.weight");
+        n_v_ = leaf("v", "v_proj.weight");
+        n_o_ = leaf("o", "o_proj.weight");
+        n_bias_ = leaf("bias", ".bias");
+        n_hs_ = leaf("head_scale", "head_scale");
+        n_sink_ = leaf("sink", "sink");
+    }
+
+    void tensors(const std::string &p, TensorList &out) const override {
+        long long qw = (long long)g_.nh * g_.hd, kw = (long long)g_.nkv * g_.hd, vw = (long long)g_.nkv * g_.vd;
+        long long ow = (long long)g_.nh * g_.vd;
+        auto mat = [&](const std::string &leaf, long long rows, long long cols) {
+            out.emplace_back(name(p, leaf), TensorSpec{{rows, cols}, MATRIX, false});
+            if (bias_) out.emplace_back(name(p, leaf + n_bias_), TensorSpec{{rows}, PARAM, false, 0.0f, 0.02f});
+        };
+        mat(n_q_, qw, hidden_);
+        if (own_kv_) {
+            mat(n_k_, kw, hidden_);
+            mat(n_v_, vw, hidden_);
+        }
+        if (head_scale_) out.emplace_back(name(p, n_hs_), TensorSpec{{g_.nh}, PARAM, false, 1.0f, 0.1f});
+        if (sink_) out.emplace_back(name(p, n_sink_), TensorSpec{{g_.nh}, PARAM, false, 0.0f, 0.5f});
+        mat(n_o_, hidden_, ow);
+    }
+
+    void load(const std::string &p, TensorMap &t) override {
+        std::vector<DevTensor> in = {take(t, name(p, n_q_))};
+        std::vector<DevTensor> bs;
+        if (bias_) bs.push_back(take(t, name(p, n_q_ + n_bias_)));
+        if (own_kv_) {
+            in.push_back(take(t, name(p, n_k_)));
+            if (bias_) bs.push_back(take(t, name(p, n_k_ + n_bias_)));
+            in.push_back(take(t, name(p, n_v_)));
+            if (bias_) bs.push_back(take(t, name(p, n_v_ + n_bias_)));
+        }
+        w_in_ = fuse_rows(*dev, in);
+        if (bias_) {
+            // one bias vector over the fused product's columns
+            for (auto &b : bs) b.shape = {b.numel(), 1};
+            b_in_ = fuse_rows(*dev, bs);
+        }
+        if (head_scale_) temp_ = take(t, name(p, n_hs_));
+        if (sink_) sinks_ = take(t, name(p, n_sink_));
+        w_o_ = take(t, name(p, n_o_));
+        if (bias_) b_o_ = take(t, name(p, n_o_ + n_bias_));
+        g_.head_scale = head_scale_ ? (const float *)temp_.ptr : nullptr;
+        g_.sink = sink_ ? (const float *)sinks_.ptr : nullptr;
+    }
+
+    size_t weight_bytes() const override {
+        return w_in_.bytes() + w_o_.bytes() + b_in_.bytes() + b_o_.bytes() + temp_.bytes() + sinks_.bytes();
+    }
+
+    KVSpec kv_spec() const override {
+        return own_kv_ ? KVSpec{g_.nkv, g_.hd, g_.window, g_.vd} : KVSpec();
+    }
+
+    void prepare(long long) override { chunk_ = ops::attention_chunk(); }
+    bool supports(StepKind) const override { return true; }
+    bool graph_safe() const override { return true; }
+
+    Stack forward(StepContext &ctx, const void *h, LayerCache &cache) override {
+        Device &d = *ctx.dev;
+        if (!chunk_) chunk_ = ops::attention_chunk();
+        if (!cache.kv.k || cache.kv_heads != g_.nkv || cache.head_dim != g_.hd || cache.v_head_dim != g_.vd)
+            fail(JB_LLM_EINVAL, "sink_attention: the cache this layer was given does not hold keys and values "
+                                "of its head count and sizes");
+        if (own_kv_ != cache.kv.writes)
+            fail(JB_LLM_EINVAL, own_kv_ ? "sink_attention: a layer with keys and values of its own was given "
+                                          "another layer's cache"
+                                        : "sink_attention: a layer without key and value products needs "
+                                          "another layer's cache (cache_of in the run order)");
+        long long n = ctx.n_rows;
+        Stack qkv = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        Buf q = ops::qkv_bias_append(d, qkv, bias_ ? (const float *)b_in_.ptr : nullptr, ctx.row_pos, ctx.row_seq,
+                                     cache.kv, g_, ctx.dtype, own_kv_);
+        qkv.buf.reset();
+        int max_chunks = (int)(ctx.max_pos / chunk_ + 1);
+        if (g_.window) max_chunks = std::min(max_chunks, (g_.window - 1) / chunk_ + 2);
+        bool decode = ctx.kind == DECODE;
+        const int32_t *blocks = nullptr;
+        int n_blocks = 0;
+        if (!decode && ctx.dtype == BF16 && ops::attention_tc_ok(g_.nh, g_.nkv, g_.hd) && g_.vd == g_.hd &&
+            !ctx.seq_len.empty()) {
+            int per = ops::attention_block_positions(g_.nh, g_.nkv);
+            std::string key = "attention_blocks/" + std::to_string(per);
+            auto it = ctx.extras.find(key);
+            if (it == ctx.extras.end()) {
+                StepContext::Extra e;
+                e.buf = ops::attention_blocks(d, ctx.seq_row0.data(), ctx.seq_pos0.data(), ctx.seq_len.data(),
+                                              ctx.n_seqs, per, &e.n);
+                it = ctx.extras.emplace(key, std::move(e)).first;
+            }
+            blocks = it->second.buf.as<int32_t>();
+            n_blocks = it->second.n;
+        }
+        Buf a = ops::attention(d, q.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, blocks, n_blocks,
+                               decode);
+        Stack out = ops::linear(d, a.ptr, ctx.dtype, n, (long long)g_.nh * g_.vd, w_o_);
+        out.bias = bias_ ? (const float *)b_o_.ptr : nullptr;
+        return out;
+    }
+
+    Json info() const override {
+        Json o = Json::object();
+        o.set("own_kv", own_kv_);
+        o.set("v_head_dim", g_.vd);
+        return o;
+    }
+
+private:
+    static bool flag(const PartSpec &s, const char *key, bool dflt) {
+        return s.has(key) ? s.params.get(key).as_bool() : dflt;
+    }
+    long long hidden_;
+    ops::AttnGeometry g_;
+    bool bias_, head_scale_, sink_, own_kv_;
+    std::string n_q_, n_k_, n_v_, n_o_, n_bias_, n_hs_, n_sink_;
+    DevTensor w_in_, b_in_, w_o_, b_o_, temp_, sinks_;
+    int chunk_ = 0;
+};
+
 }  // namespace
 
 void register_builtin_mixers() {
+    register_part("mixer", "sink_attention", [](const PartSpec &s, DType dt, Device *d) {
+        return std::unique_ptr<Part>(new SinkAttention(s, dt, d));
+    });
     register_part("mixer", "gqa_attention", [](const PartSpec &s, DType dt, Device *d) {
         return std::unique_ptr<Part>(new GQAAttention(s, dt, d));
     });

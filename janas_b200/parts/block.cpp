@@ -1,5 +1,11 @@
-// Block arrangements.  prenorm: x += mixer(norm(x)); x += ffn(norm(x))
-// (src/llm/model.c:743-796).
+// Block arrangements.
+//
+// prenorm: x += mixer(norm(x)); x += ffn(norm(x))  (src/llm/model.c:743-796).
+//
+// sandwich: a norm before and after each sublayer, and optionally a gate on the
+// sublayer's result, computed from the sublayer's own input:
+//     h = norm_in(x);  y = sublayer(h);  y *= sigmoid(G h + g);  x += norm_out(y)
+// for the mixer and then, where the layer has one, for the feed-forward.
 #include "part.h"
 
 namespace jb {
@@ -8,7 +14,10 @@ namespace {
 
 class PreNormBlock : public Block {
 public:
-    using Block::Block;
+    explicit PreNormBlock(BlockParts p) : Block(std::move(p)) {
+        if (!feed_forward || !ffn_norm) config_error("prenorm: the layer needs a feed-forward and its norm");
+        if (post_mixer_norm || post_ffn_norm) config_error("prenorm: the arrangement has no norms on results");
+    }
     void forward(StepContext &ctx, float *x, Stack &pending, LayerCache &cache) override {
         long long n = ctx.n_rows;
         // the add of what the previous part produced is fused into the norm
@@ -19,12 +28,142 @@ public:
     }
 };
 
+// block_params: hidden_size; mixer_gate / ffn_gate: the tensor names (below the
+// layer's prefix) of the gates' matrices [hidden, hidden], absent or null for no
+// gate; gate_bias: the suffix of a gate's bias vector ("" for none).
+class SandwichBlock : public Block {
+public:
+    SandwichBlock(BlockParts p, const LayerSpec &ls, DType dt, Device *d) : Block(std::move(p)), dev_(d) {
+        if (!post_mixer_norm || (feed_forward && !post_ffn_norm))
+            config_error("sandwich: every sublayer needs a norm on its result");
+        const Json &bp = ls.block_params;
+        hidden_ = bp.get("hidden_size").is_number() ? bp.get("hidden_size").as_int() : mixer_norm->size();
+        if (bp.get("mixer_gate").is_string()) gate_name_[0] = bp.get("mixer_gate").as_string();
+        if (bp.get("ffn_gate").is_string() && feed_forward) gate_name_[1] = bp.get("ffn_gate").as_string();
+        if (bp.get("gate_bias").is_string()) bias_suffix_ = bp.get("gate_bias").as_string();
+        // tensors of an absent feed-forward's surroundings that a file may still
+        // hold: tolerated and not read
+        if (!feed_forward)
+            for (auto &v : bp.get("unused").items())
+                if (v.is_object() && v.get("name").is_string()) {
+                    std::vector<long long> shape;
+                    for (auto &s : v.get("shape").items()) shape.push_back(s.as_int());
+                    unused_.emplace_back(v.get("name").as_string(), shape);
+                }
+    }
+
+    void tensors(const std::string &prefix, TensorList &out) const override {
+        for (int i = 0; i < 2; i++) {
+            if (gate_name_[i].empty()) continue;
+            out.emplace_back(Part::name(prefix, gate_name_[i]), TensorSpec{{hidden_, hidden_}, MATRIX, false});
+            if (!bias_suffix_.empty())
+                out.emplace_back(Part::name(prefix, gate_name_[i] + bias_suffix_),
+                                 TensorSpec{{hidden_}, PARAM, false, 0.0f, 0.02f});
+        }
+        for (auto &u : unused_)
+            out.emplace_back(Part::name(prefix, u.first),
+                             TensorSpec{u.second, u.second.size() == 2 ? MATRIX : PARAM, true});
+    }
+
+    void load(const std::string &prefix, TensorMap &t) override {
+        for (int i = 0; i < 2; i++) {
+            if (gate_name_[i].empty()) continue;
+            gate_[i] = Part::take(t, Part::name(prefix, gate_name_[i]));
+            if (!bias_suffix_.empty()) gate_bias_[i] = Part::take(t, Part::name(prefix, gate_name_[i] + bias_suffix_));
+        }
+        for (auto &u : unused_) t.erase(Part::name(prefix, u.first));
+    }
+
+    size_t weight_bytes() const override {
+        return gate_[0].bytes() + gate_[1].bytes() + gate_bias_[0].bytes() + gate_bias_[1].bytes();
+    }
+
+    void forward(StepContext &ctx, float *x, Stack &pending, LayerCache &cache) override {
+        long long n = ctx.n_rows;
+        Buf h = take_normed(ctx, mixer_norm.get());
+        if (!h) h = mixer_norm->apply(ctx, x, n, ctx.dtype, pending ? &pending : nullptr, nullptr, 0);
+        else if (pending) fail(JB_LLM_EFAIL, "sandwich: a norm was computed ahead of a pending sum");
+        pending = Stack();
+        {
+            Stack g = gate_product(ctx, 0, h.ptr);
+            Stack y = mixer->forward(ctx, h.ptr, cache);
+            const Norm *next = feed_forward ? ffn_norm.get() : next_norm;
+            finish(ctx, x, y, g, 0, post_mixer_norm.get(), next);
+        }
+        if (!feed_forward) return;
+        h = take_normed(ctx, ffn_norm.get());
+        if (!h) h = ffn_norm->apply(ctx, x, n, ctx.dtype, nullptr, nullptr, 0);
+        {
+            Stack g = gate_product(ctx, 1, h.ptr);
+            Stack y = feed_forward->forward(ctx, h.ptr);
+            finish(ctx, x, y, g, 1, post_ffn_norm.get(), next_norm);
+        }
+    }
+
+private:
+    static Buf take_normed(StepContext &ctx, const Norm *by) {
+        if (!ctx.normed || ctx.normed_by != by) {
+            ctx.normed.reset();
+            ctx.normed_by = nullptr;
+            return Buf();
+        }
+        ctx.normed_by = nullptr;
+        return std::move(ctx.normed);
+    }
+
+    Stack gate_product(StepContext &ctx, int which, const void *h) {
+        if (!gate_[which]) return Stack();
+        return ops::linear(*ctx.dev, h, ctx.dtype, ctx.n_rows, hidden_, gate_[which]);
+    }
+
+    // x += norm_out(y * gate); the next norm of x too where both norms work value by
+    // value (its result then waits in ctx.normed)
+    void finish(StepContext &ctx, float *x, Stack &y, const Stack &g, int which, Norm *post, const Norm *next) {
+        Device &d = *ctx.dev;
+        long long n = ctx.n_rows;
+        const float *g_bias = gate_bias_[which] ? (const float *)gate_bias_[which].ptr : nullptr;
+        ops::DytParams pp, np;
+        if (g && post->dynamic_tanh(&pp)) {
+            bool fuse_next = next && next->dynamic_tanh(&np);
+            Buf out = ops::gated_dyt_residual(d, x, y, g, 0, g_bias, pp, fuse_next ? &np : nullptr, ctx.dtype);
+            if (fuse_next) {
+                ctx.normed = std::move(out);
+                ctx.normed_by = next;
+            }
+            return;
+        }
+        // the steps one by one, for any norm: gate, norm of the result, add
+        Buf t;
+        Stack one;
+        if (g) {
+            t = ops::gate_mul(d, y, g, 0, g_bias);
+        } else {
+            t = d.pool.get((size_t)n * (size_t)hidden_ * 4);
+            cuda_check(cudaMemsetAsync(t.ptr, 0, t.bytes, d.stream), "clearing a sum");
+            ops::add_(d, t.as<float>(), n, hidden_, y);
+        }
+        one.buf = post->apply(ctx, t.as<float>(), n, F32, nullptr, nullptr, 0);
+        one.S = 1;
+        one.n = n;
+        one.m = hidden_;
+        ops::add_(d, x, n, hidden_, one);
+    }
+
+    Device *dev_;
+    long long hidden_ = 0;
+    std::string gate_name_[2], bias_suffix_;
+    DevTensor gate_[2], gate_bias_[2];
+    std::vector<std::pair<std::string, std::vector<long long>>> unused_;
+};
+
 }  // namespace
 
 void register_builtin_blocks() {
-    register_block("prenorm", [](std::unique_ptr<Mixer> m, std::unique_ptr<FeedForward> f,
-                                 std::unique_ptr<Norm> n1, std::unique_ptr<Norm> n2) {
-        return std::unique_ptr<Block>(new PreNormBlock(std::move(m), std::move(f), std::move(n1), std::move(n2)));
+    register_block("prenorm", [](BlockParts p, const LayerSpec &, DType, Device *) {
+        return std::unique_ptr<Block>(new PreNormBlock(std::move(p)));
+    });
+    register_block("sandwich", [](BlockParts p, const LayerSpec &ls, DType dt, Device *d) {
+        return std::unique_ptr<Block>(new SandwichBlock(std::move(p), ls, dt, d));
     });
 }
 

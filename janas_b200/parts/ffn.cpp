@@ -76,9 +76,63 @@ private:
     bool fused_last_ = false;      // whether the last forward took the one-kernel way
 };
 
+// A dense feed-forward with the PolyNorm activation: down(act(up(x))), no biases,
+//   act(z) = c0 n(z) + c1 n(z^2) + c2 n(z^3) + c3,   n(u) = u / sqrt(mean(u^2) + eps)
+// with powers value by value, the mean over one token's feed-forward values, and
+// the four numbers c learned.
+// params: hidden_size, intermediate_size, eps, names (optional): up, down, coefficients
+class PolyNormFFN : public FeedForward {
+public:
+    PolyNormFFN(const PartSpec &s, DType dt, Device *d) : FeedForward(s, dt, d) {
+        hidden_ = s.get_int("hidden_size");
+        inter_ = s.get_int("intermediate_size");
+        eps_ = (float)s.get_double("eps");
+        if (hidden_ <= 0 || inter_ <= 0) config_error("polynorm: sizes must be positive");
+        const Json &nm = s.params.get("names");
+        auto leaf = [&](const char *key, const char *dflt) {
+            return nm.is_object() && nm.get(key).is_string() ? nm.get(key).as_string() : std::string(dflt);
+        };
+        n_up_ = leaf("up", "up_proj.weight");
+        n_down_ = leaf("down", "down_proj.weight");
+        n_coef_ = leaf("coefficients", "act.weight");
+    }
+
+    void tensors(const std::string &prefix, TensorList &out) const override {
+        out.emplace_back(name(prefix, n_up_), TensorSpec{{inter_, hidden_}, MATRIX, false});
+        out.emplace_back(name(prefix, n_down_), TensorSpec{{hidden_, inter_}, MATRIX, false});
+        out.emplace_back(name(prefix, n_coef_), TensorSpec{{4}, PARAM, false, 0.3f, 0.1f});
+    }
+
+    void load(const std::string &prefix, TensorMap &t) override {
+        w_up_ = take(t, name(prefix, n_up_));
+        w_down_ = take(t, name(prefix, n_down_));
+        coef_ = take(t, name(prefix, n_coef_));
+    }
+
+    size_t weight_bytes() const override { return w_up_.bytes() + w_down_.bytes() + coef_.bytes(); }
+
+    Stack forward(StepContext &ctx, const void *h) override {
+        Device &d = *ctx.dev;
+        long long n = ctx.n_rows;
+        Stack z = ops::linear(d, h, ctx.dtype, n, hidden_, w_up_);
+        Buf act = ops::polynorm(d, z, inter_, (const float *)coef_.ptr, eps_, ctx.dtype);
+        z.buf.reset();
+        return ops::linear(d, act.ptr, ctx.dtype, n, inter_, w_down_);
+    }
+
+private:
+    long long hidden_, inter_;
+    float eps_;
+    std::string n_up_, n_down_, n_coef_;
+    DevTensor w_up_, w_down_, coef_;
+};
+
 }  // namespace
 
 void register_builtin_feed_forwards() {
+    register_part("feed_forward", "polynorm", [](const PartSpec &s, DType dt, Device *d) {
+        return std::unique_ptr<Part>(new PolyNormFFN(s, dt, d));
+    });
     register_part("feed_forward", "swiglu", [](const PartSpec &s, DType dt, Device *d) {
         return std::unique_ptr<Part>(new SwiGLU(s, dt, d));
     });

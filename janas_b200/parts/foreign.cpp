@@ -76,6 +76,7 @@ Json cache_json(const LayerCache &c) {
     o.set("n_pages", c.kv.n_pages);
     o.set("kv_heads", c.kv_heads);
     o.set("head_dim", c.head_dim);
+    o.set("v_head_dim", c.v_head_dim);
     o.set("page", PAGE);
     o.set("dtype", dtype_name(c.kv.dt));
     o.set("block_table", addr(c.kv.block_table));

@@ -44,9 +44,72 @@ private:
     DevTensor weight_;
 };
 
+// Dynamic Tanh: out = tanh(alpha x) w + b, value by value; no mean and no
+// variance is computed.  alpha is one number.
+// params: size; names (optional): weight, bias, alpha: the tensors' leaves below the
+// part's prefix ("" for the prefix itself)
+class DynamicTanh : public Norm {
+public:
+    DynamicTanh(const PartSpec &s, DType dt, Device *d) : Norm(s, dt, d) {
+        size_ = s.get_int("size");
+        if (size_ <= 0) config_error("dynamic_tanh: size must be positive");
+        const Json &nm = s.params.get("names");
+        auto leaf = [&](const char *key, const char *dflt) {
+            return nm.is_object() && nm.get(key).is_string() ? nm.get(key).as_string() : std::string(dflt);
+        };
+        w_name_ = leaf("weight", "weight");
+        b_name_ = leaf("bias", "bias");
+        a_name_ = leaf("alpha", "alpha");
+    }
+
+    void tensors(const std::string &prefix, TensorList &out) const override {
+        out.emplace_back(name(prefix, w_name_), TensorSpec{{size_}, PARAM, false, 1.0f, 0.1f});
+        out.emplace_back(name(prefix, b_name_), TensorSpec{{size_}, PARAM, false, 0.0f, 0.02f});
+        out.emplace_back(name(prefix, a_name_), TensorSpec{{}, PARAM, false, 0.5f, 0.05f});
+    }
+
+    void load(const std::string &prefix, TensorMap &t) override {
+        w_ = take(t, name(prefix, w_name_));
+        b_ = take(t, name(prefix, b_name_));
+        alpha_ = take(t, name(prefix, a_name_));
+    }
+
+    size_t weight_bytes() const override { return w_.bytes() + b_.bytes() + alpha_.bytes(); }
+
+    Buf apply(StepContext &ctx, float *x, long long n, DType out_dt, const Stack *delta, const int32_t *rows,
+              long long n_out) override {
+        ops::DytParams p;
+        dynamic_tanh(&p);
+        return ops::dyt(*ctx.dev, x, n, size_, p, out_dt, delta, rows, n_out);
+    }
+
+    bool dynamic_tanh(ops::DytParams *out) const override {
+        out->w = (const float *)w_.ptr;
+        out->b = (const float *)b_.ptr;
+        out->alpha = (const float *)alpha_.ptr;
+        return true;
+    }
+
+    long long size() const override { return size_; }
+
+    Json info() const override {
+        Json o = Json::object();
+        o.set("size", size_);
+        return o;
+    }
+
+private:
+    long long size_;
+    std::string w_name_, b_name_, a_name_;
+    DevTensor w_, b_, alpha_;
+};
+
 }  // namespace
 
 void register_builtin_norms() {
+    register_part("norm", "dynamic_tanh", [](const PartSpec &s, DType dt, Device *d) {
+        return std::unique_ptr<Part>(new DynamicTanh(s, dt, d));
+    });
     register_part("norm", "rmsnorm", [](const PartSpec &s, DType dt, Device *d) {
         return std::unique_ptr<Part>(new RMSNorm(s, dt, d));
     });

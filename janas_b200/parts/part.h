@@ -39,10 +39,12 @@ enum StepKind {
 };
 const char *step_kind_name(StepKind k);
 
+class Norm;
+
 // What a mixer sees of the cache for the run-order entry it runs as.
 struct LayerCache {
     ops::AttnCache kv;                  // this entry's K/V pages and the step's block table
-    int kv_heads = 0, head_dim = 0;
+    int kv_heads = 0, head_dim = 0, v_head_dim = 0;
     void *state = nullptr;              // [slots, *state shape], indexed by slot; or null
     StateSpec state_spec;
     int n_slots = 0;
@@ -75,6 +77,11 @@ struct StepContext {
     // what a part computed once for all layers of this step (the attention's blocks)
     struct Extra { Buf buf; int n = 0; };
     std::map<std::string, Extra> extras;
+    // The next norm of the residual stream, when the block that ran last computed
+    // it with its own last step (see Block::next_norm); taken by whoever applies
+    // that norm next.
+    Buf normed;
+    const Norm *normed_by = nullptr;
 };
 
 using TensorMap = std::map<std::string, DevTensor>;
@@ -95,8 +102,9 @@ public:
     DType dtype;
     Device *dev;
 
+    // an empty leaf names the prefix itself (a tensor called as its part is)
     static std::string name(const std::string &prefix, const std::string &leaf) {
-        return prefix.empty() ? leaf : prefix + "." + leaf;
+        return prefix.empty() ? leaf : leaf.empty() ? prefix : prefix + "." + leaf;
     }
     // the tensor `name` out of the map (it is erased there); Error when it is missing
     static DevTensor take(TensorMap &t, const std::string &name);
@@ -112,6 +120,10 @@ public:
     virtual Buf apply(StepContext &ctx, float *x, long long n, DType out_dt, const Stack *delta,
                       const int32_t *rows, long long n_out) = 0;
     virtual long long size() const = 0;
+    // A norm that works value by value as tanh(alpha x) w + b says so here and gives
+    // its parameters, so that a block can take it into the kernel that ends a
+    // sublayer; every other norm answers false.
+    virtual bool dynamic_tanh(ops::DytParams *out) const { return false; }
 };
 
 class PositionEncoding : public Part {
@@ -150,14 +162,34 @@ public:
     virtual Stack forward(StepContext &ctx, const void *h) = 0;
 };
 
-// The arrangement of one layer's parts around the residual stream.
+// The parts of one layer as they are handed to its arrangement.  feed_forward and
+// ffn_norm are null for a layer without a feed-forward; the two post norms (on a
+// sublayer's result, before it joins the residual stream) are null where the
+// layer's spec names none.
+struct BlockParts {
+    std::unique_ptr<Mixer> mixer;
+    std::unique_ptr<FeedForward> feed_forward;
+    std::unique_ptr<Norm> mixer_norm, ffn_norm, post_mixer_norm, post_ffn_norm;
+};
+
+// The arrangement of one layer's parts around the residual stream.  An
+// arrangement may own tensors itself (gates on the residual branches), named below
+// the layer's prefix like a part's.
 class Block {
 public:
-    Block(std::unique_ptr<Mixer> m, std::unique_ptr<FeedForward> f, std::unique_ptr<Norm> n1,
-          std::unique_ptr<Norm> n2)
-        : mixer(std::move(m)), feed_forward(std::move(f)), mixer_norm(std::move(n1)),
-          ffn_norm(std::move(n2)) {}
+    explicit Block(BlockParts p)
+        : mixer(std::move(p.mixer)), feed_forward(std::move(p.feed_forward)),
+          mixer_norm(std::move(p.mixer_norm)), ffn_norm(std::move(p.ffn_norm)),
+          post_mixer_norm(std::move(p.post_mixer_norm)), post_ffn_norm(std::move(p.post_ffn_norm)) {}
     virtual ~Block() = default;
+    virtual void tensors(const std::string &prefix, TensorList &out) const {}
+    virtual void load(const std::string &prefix, TensorMap &t) {}
+    virtual size_t weight_bytes() const { return 0; }
+    // The norm the NEXT thing applies to the residual stream after this layer
+    // (the next layer's first norm, or the model's last one), or null; a block may
+    // compute it together with its own last step and leave the result in
+    // ctx.normed.  Set by the model before each forward.
+    const Norm *next_norm = nullptr;
     // x: the float32 residual stream [n, hidden], updated in place; pending: a
     // stack of partial sums not yet added to x (empty for none), replaced by what
     // this layer leaves to be added.
@@ -165,13 +197,12 @@ public:
 
     std::unique_ptr<Mixer> mixer;
     std::unique_ptr<FeedForward> feed_forward;
-    std::unique_ptr<Norm> mixer_norm, ffn_norm;
+    std::unique_ptr<Norm> mixer_norm, ffn_norm, post_mixer_norm, post_ffn_norm;
 };
 
 // ------------------------------------------------------------------ registry
 using PartFactory = std::function<std::unique_ptr<Part>(const PartSpec &, DType, Device *)>;
-using BlockFactory = std::function<std::unique_ptr<Block>(
-    std::unique_ptr<Mixer>, std::unique_ptr<FeedForward>, std::unique_ptr<Norm>, std::unique_ptr<Norm>)>;
+using BlockFactory = std::function<std::unique_ptr<Block>(BlockParts, const LayerSpec &, DType, Device *)>;
 
 // role: "mixer", "feed_forward", "norm" or "position"
 void register_part(const std::string &role, const std::string &kind, PartFactory f);
@@ -183,9 +214,8 @@ std::unique_ptr<Mixer> build_mixer(const PartSpec &spec, DType dt, Device *dev);
 std::unique_ptr<FeedForward> build_feed_forward(const PartSpec &spec, DType dt, Device *dev);
 std::unique_ptr<Norm> build_norm(const PartSpec &spec, DType dt, Device *dev);
 std::unique_ptr<PositionEncoding> build_position(const PartSpec &spec, DType dt, Device *dev);
-std::unique_ptr<Block> build_block(const std::string &kind, std::unique_ptr<Mixer> m,
-                                   std::unique_ptr<FeedForward> f, std::unique_ptr<Norm> n1,
-                                   std::unique_ptr<Norm> n2);
+// Builds the layer's parts from its spec and hands them to the arrangement it names.
+std::unique_ptr<Block> build_block(const LayerSpec &ls, DType dt, Device *dev);
 
 // Several matrices over the same input as one, rows one after the other, so that
 // one product serves them all (the reference dispatches q, k, v as one group and

@@ -100,9 +100,8 @@ std::unique_ptr<PositionEncoding> build_position(const PartSpec &s, DType dt, De
     return as_role<PositionEncoding>(build_part("position", s, dt, d), "position", s);
 }
 
-std::unique_ptr<Block> build_block(const std::string &kind, std::unique_ptr<Mixer> m,
-                                   std::unique_ptr<FeedForward> f, std::unique_ptr<Norm> n1,
-                                   std::unique_ptr<Norm> n2) {
+std::unique_ptr<Block> build_block(const LayerSpec &ls, DType dt, Device *dev) {
+    const std::string &kind = ls.block;
     BlockFactory bf;
     {
         Tables &t = ready();
@@ -115,7 +114,16 @@ std::unique_ptr<Block> build_block(const std::string &kind, std::unique_ptr<Mixe
         }
         bf = it->second;
     }
-    return bf(std::move(m), std::move(f), std::move(n1), std::move(n2));
+    BlockParts p;
+    p.mixer = build_mixer(ls.mixer, dt, dev);
+    p.mixer_norm = build_norm(ls.mixer_norm, dt, dev);
+    if (!ls.feed_forward.kind.empty()) {
+        p.feed_forward = build_feed_forward(ls.feed_forward, dt, dev);
+        p.ffn_norm = build_norm(ls.ffn_norm, dt, dev);
+    }
+    if (!ls.post_mixer_norm.kind.empty()) p.post_mixer_norm = build_norm(ls.post_mixer_norm, dt, dev);
+    if (!ls.post_ffn_norm.kind.empty() && p.feed_forward) p.post_ffn_norm = build_norm(ls.post_ffn_norm, dt, dev);
+    return bf(std::move(p), ls, dt, dev);
 }
 
 DevTensor Part::take(TensorMap &t, const std::string &name) {

@@ -15,7 +15,7 @@ import numpy as np
 from .. import lib
 from .random_init import random_tensor, random_tensors, write_random_model
 from .safetensors_io import SafetensorsError, write_safetensors
-from .spec import EMBEDDING, INT_TABLE, MATRIX, NORM, TensorSpec
+from .spec import EMBEDDING, INT_TABLE, MATRIX, NORM, PARAM, TensorSpec
 
 
 class WeightError(ValueError):
@@ -31,13 +31,14 @@ class WeightError(ValueError):
 
 
 def _list_json(expected: Mapping[str, TensorSpec]) -> list:
-    return [{"name": n, "shape": list(s.shape), "kind": s.kind, "optional": s.optional}
-            for n, s in expected.items()]
+    return [{"name": n, "shape": list(s.shape), "kind": s.kind, "optional": s.optional,
+             "mean": s.mean, "std": s.std} for n, s in expected.items()]
 
 
 def tensor_list(items) -> Dict[str, TensorSpec]:
     """The library's tensor list (JSON) as name -> TensorSpec, in its order."""
-    return {t["name"]: TensorSpec(tuple(t["shape"]), t["kind"], t["optional"]) for t in items}
+    return {t["name"]: TensorSpec(tuple(t["shape"]), t["kind"], t["optional"], t.get("mean", 0.0),
+                                  t.get("std", 0.02)) for t in items}
 
 
 def expected_tensors(spec) -> Dict[str, TensorSpec]:
@@ -88,7 +89,7 @@ def read_tensor(model_dir: str, name: str, dtype: str, shape) -> np.ndarray:
     return out
 
 
-__all__ = ["EMBEDDING", "INT_TABLE", "MATRIX", "NORM", "SafetensorsError", "TensorSpec",
+__all__ = ["EMBEDDING", "INT_TABLE", "MATRIX", "NORM", "PARAM", "SafetensorsError", "TensorSpec",
            "WeightError", "check_folder", "expected_tensors", "list_folder", "random_tensor",
            "random_tensors", "read_tensor", "resident_dtype", "tensor_list", "write_random_model",
            "write_safetensors"]

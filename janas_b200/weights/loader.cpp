@@ -12,6 +12,7 @@ const char *kind_name(TensorKind k) {
         case EMBEDDING: return "embedding";
         case NORM: return "norm";
         case INT_TABLE: return "int_table";
+        case PARAM: return "param";
     }
     return "?";
 }
@@ -21,6 +22,7 @@ TensorKind parse_kind(const std::string &s) {
     if (s == "embedding") return EMBEDDING;
     if (s == "norm") return NORM;
     if (s == "int_table") return INT_TABLE;
+    if (s == "param") return PARAM;
     fail(JB_LLM_EINVAL, "unknown tensor kind '" + s + "'");
 }
 
@@ -38,6 +40,10 @@ Json tensor_list_json(const TensorList &l) {
         o.set("shape", shape_json(kv.second.shape));
         o.set("kind", kind_name(kv.second.kind));
         o.set("optional", kv.second.optional);
+        if (kv.second.kind == PARAM) {
+            o.set("mean", (double)kv.second.mean);
+            o.set("std", (double)kv.second.std);
+        }
         a.push(o);
     }
     return a;
@@ -51,6 +57,8 @@ TensorList tensor_list_from_json(const Json &j) {
         for (auto &v : o.get("shape").items()) s.shape.push_back(v.as_int());
         s.kind = o.get("kind").is_string() ? parse_kind(o.get("kind").as_string()) : MATRIX;
         s.optional = o.get("optional").as_bool();
+        if (o.get("mean").is_number()) s.mean = (float)o.get("mean").as_double();
+        if (o.get("std").is_number()) s.std = (float)o.get("std").as_double();
         l.emplace_back(o.get("name").as_string(), s);
     }
     return l;
@@ -83,7 +91,7 @@ Json WeightMismatch::to_json() const {
 
 DType resident_dtype(const std::string &stored, TensorKind kind, DType compute) {
     if (kind == INT_TABLE) return I32;
-    if (compute == F32 || stored == "F32") return F32;
+    if (compute == F32 || stored == "F32" || kind == PARAM) return F32;
     return BF16;
 }
 
@@ -245,8 +253,10 @@ DevTensor random_tensor(Device &dev, const std::string &name, const TensorSpec &
     if (spec.kind == INT_TABLE) fail(JB_LLM_EINVAL, name + ": no random rule for integer tables");
     if (dt != F32 && dt != BF16) fail(JB_LLM_EINVAL, "random weights are made as bfloat16 or float32");
     dev.make_current();
+    if (spec.kind == PARAM) dt = F32;
     DevTensor t = dev.tensor(dt, spec.shape);
     float mean = spec.kind == NORM ? 1.0f : 0.0f, std = spec.kind == NORM ? 0.1f : 0.02f;
+    if (spec.kind == PARAM) { mean = spec.mean; std = spec.std; }
     int rc = jb_fill_normal(t.ptr, (int)dt, t.numel(), tensor_seed(seed, name), mean, std, dev.stream);
     if (rc != 0) fail(JB_LLM_EFAIL, name + ": the random fill could not be launched");
     return t;

@@ -25,7 +25,9 @@
 namespace jb {
 
 // kinds of tensors; they decide the resident dtype and the random distribution
-enum TensorKind { MATRIX, EMBEDDING, NORM, INT_TABLE };
+// PARAM: a small vector or scalar of constants (biases, per-head numbers, a norm's
+// alpha); always kept in float32, whatever it is stored as.
+enum TensorKind { MATRIX, EMBEDDING, NORM, INT_TABLE, PARAM };
 const char *kind_name(TensorKind k);
 TensorKind parse_kind(const std::string &s);
 
@@ -33,6 +35,11 @@ struct TensorSpec {
     std::vector<long long> shape;
     TensorKind kind = MATRIX;
     bool optional = false;          // absent is allowed (a tied head)
+    // random weights: N(mean, std) for a PARAM (the other kinds have fixed rules)
+    float mean = 0.0f, std = 0.02f;
+    TensorSpec() = default;
+    TensorSpec(std::vector<long long> s, TensorKind k, bool opt, float m = 0.0f, float sd = 0.02f)
+        : shape(std::move(s)), kind(k), optional(opt), mean(m), std(sd) {}
 };
 
 // name -> spec, in the order the model names them

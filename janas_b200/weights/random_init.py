@@ -16,7 +16,7 @@ from typing import Iterator, Mapping, Tuple
 import torch
 
 from .safetensors_io import write_safetensors
-from .spec import EMBEDDING, INT_TABLE, MATRIX, NORM, TensorSpec
+from .spec import EMBEDDING, INT_TABLE, MATRIX, NORM, PARAM, TensorSpec
 
 MATRIX_STD = 0.02
 NORM_STD = 0.1
@@ -41,6 +41,8 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype,
         t.mul_(NORM_STD).add_(1.0)
     elif spec.kind in (MATRIX, EMBEDDING):
         t.mul_(MATRIX_STD)
+    elif spec.kind == PARAM:
+        t.mul_(spec.std).add_(spec.mean)
     else:
         raise ValueError(f"{name}: unknown tensor kind {spec.kind}")
     return t.to(dtype)
