@@ -70,7 +70,8 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q,
                     const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
                     const int32_t *__restrict__ block_table, int bt_stride,
                     float *__restrict__ part, int nh, int nkv, int G, int window, float scale,
-                    int max_chunks, int chunks_per_cta, int row0)
+                    int max_chunks, int chunks_per_cta, int row0,
+                    const float *__restrict__ head_scale)
 {
     using Cfg = AttnCfg<HD>;
     constexpr int NB = Cfg::NB;
@@ -221,7 +222,9 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q,
         bool warp_live = __any_sync(0xffffffffu, live);
         int pos = q_pos;
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
-        const float c2 = scale * 1.4426950408889634f;      // scores in units of log2(e)
+        // scores in units of log2(e); a head may have a factor of its own
+        const float c2 = scale * 1.4426950408889634f *
+                         (head_scale != nullptr && live ? head_scale[kvh * G + g] : 1.0f);
         bool ok = true;
         for (int it = 0; it < n_chunks; it++) {
             int c = c_first + it;
@@ -364,7 +367,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_v, const int32_t *__restrict__ qblk,
                        const int32_t *__restrict__ block_table, int bt_stride,
                        bf16 *__restrict__ out, int nh, int nkv, int G, int R, int window,
-                       float scale)
+                       float scale, const float *__restrict__ head_scale,
+                       const float *__restrict__ sink)
 {
     using Cfg = PrefillCfg<HD>;
     constexpr int NB = Cfg::NB;
@@ -561,7 +565,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
         uint32_t tmem_s = tmem + t * AT_KEYS + lane_addr;
         uint32_t tmem_o = tmem + 2 * AT_KEYS + t * HD + lane_addr;
-        const float c2 = scale * 1.4426950408889634f;      // scores in units of log2(e)
+        // scores in units of log2(e); a head may have a factor of its own (positive:
+        // the maximum below is taken before the factor is applied)
+        const float c2 = scale * 1.4426950408889634f *
+                         (head_scale != nullptr && live ? head_scale[kvh * G + g] : 1.0f);
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (int it = 0; it < n_chunks && tile_live; it++) {
@@ -667,6 +674,18 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
             float inv = 1.0f / l_run;
+            if (sink != nullptr && live) {
+                // the head's sink joins the denominator: 2^(sink - m) beside l, with the
+                // larger of the two as the reference so that neither overflows
+                float s2 = sink[kvh * G + g] * 1.4426950408889634f;
+                float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+                if (s2 > m_use) {
+                    float a = exp2f(m_use - s2);
+                    inv = a / fmaf(l_run, a, 1.0f);
+                } else {
+                    inv = 1.0f / (l_run + exp2f(s2 - m_use));
+                }
+            }
             bf16 *dst = out + ((size_t)(q_row + jq) * nh + kvh * G + g) * HD;
 #pragma unroll 1
             for (int db = 0; db < HD / 32; db++) {
@@ -733,6 +752,9 @@ struct DecodeQkv {
     const float *cs, *sn;        // rotation tables [positions][HD / 2], or nullptr
     bf16 *k_cache, *v_cache;     // where the new key and value go, or nullptr (a layer that
                                  // reads another layer's cache)
+    const float *bias;           // the product's bias over its columns, or nullptr
+    const float *head_scale;     // a factor per head on the scores, or nullptr (also without qkv)
+    long long ld;                // floats from one row of qkv to the next; 0: (nh + 2 nkv) HD
 };
 
 __device__ __forceinline__ float4 load_w4(const void *w, int w_f32, int at)
@@ -855,7 +877,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     if (fused && warp >= 2) {
         int n_slots = G + (appends ? 2 : 0);        // q heads, then the key, then the value
         int all_slots = nh + 2 * nkv;
-        const float *src_row = f.qkv + (size_t)q_row * all_slots * HD;
+        const float *src_row = f.qkv + (size_t)q_row * (f.ld > 0 ? (size_t)f.ld : (size_t)all_slots * HD);
         for (int base = 0; base < n_slots; base += 8) {
             int slot = base + (warp - 2) * 2 + (lane >> 4);
             bool live = slot < n_slots;
@@ -878,6 +900,12 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                             lo.x += a[u].x; lo.y += a[u].y; lo.z += a[u].z; lo.w += a[u].w;
                             hi.x += b[u].x; hi.y += b[u].y; hi.z += b[u].z; hi.w += b[u].w;
                         }
+                }
+                if (f.bias != nullptr) {
+                    float4 a = load4(f.bias + (size_t)hs * HD + at4);
+                    float4 b = load4(f.bias + (size_t)hs * HD + HD / 2 + at4);
+                    lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+                    hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
                 }
             }
             float ss = lo.x * lo.x;
@@ -1038,7 +1066,11 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         int qw = warp & 3;
         int r = qw * 32 + lane;                 // this thread's key of the chunk, then its value
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
-        const float c2 = scale * 1.4426950408889634f;
+        float c2[GP];
+#pragma unroll
+        for (int g = 0; g < GP; g++)
+            c2[g] = scale * 1.4426950408889634f *
+                    (f.head_scale != nullptr && g < G ? f.head_scale[kvh * G + g] : 1.0f);
         bool ok = true;
         // running over this CTA's chunks: maximum, sum (every thread keeps all heads')
         // and this thread's value of O for every head
@@ -1077,7 +1109,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                 tc_ld16(tmem_s + (it & 1) * DQ_N + lane_addr, sc);
 #pragma unroll
             for (int g = 0; g < GP; g++) {
-                float v = (ok && visible && g < G) ? sc[g] * c2 : -INFINITY;
+                float v = (ok && visible && g < G) ? sc[g] * c2[g] : -INFINITY;
                 sc[g] = v;
                 m[g] = warp_max(v);
             }
@@ -1206,7 +1238,7 @@ static int launch_attn_rows(const void *q, const void *k_cache, const void *v_ca
                             long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
                             const int32_t *block_table, int bt_stride, float *part, int n, int nh,
                             int nkv, int window, float scale, int max_chunks, int chunks_per_cta,
-                            int row0, int n_rows, cudaStream_t st)
+                            int row0, int n_rows, const float *head_scale, cudaStream_t st)
 {
     using Cfg = AttnCfg<HD>;
     int G = nh / nkv;
@@ -1224,7 +1256,7 @@ static int launch_attn_rows(const void *q, const void *k_cache, const void *v_ca
         return JB_OK;
     launch(kern, dim3(gx, nkv), 192, Cfg::SMEM_BYTES, st, mq, mk, mv, row_pos, row_seq,
            block_table, bt_stride, part, nh, nkv, G, window, scale, max_chunks, chunks_per_cta,
-           row0);
+           row0, head_scale);
     return launch_status();
 }
 
@@ -1256,6 +1288,20 @@ extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void
                                   const int32_t *block_table, int bt_stride, void *out, int n,
                                   int nh, int nkv, int hd, int window, float scale, cudaStream_t st)
 {
+    return jb_attn_tc_prefill_sink(q, k_cache, v_cache, n_pages, qblk, n_blocks, block_table,
+                                   bt_stride, out, n, nh, nkv, hd, window, scale, nullptr, nullptr,
+                                   st);
+}
+
+// The same with a factor per head on the scores (head_scale, float [nh], every one
+// positive, or null) and a sink per head in the softmax's denominator (sink, float
+// [nh], or null).
+extern "C" int jb_attn_tc_prefill_sink(const void *q, const void *k_cache, const void *v_cache,
+                                       long long n_pages, const int32_t *qblk, int n_blocks,
+                                       const int32_t *block_table, int bt_stride, void *out, int n,
+                                       int nh, int nkv, int hd, int window, float scale,
+                                       const float *head_scale, const float *sink, cudaStream_t st)
+{
     if (!jb_attn_tc_ok(nh, nkv, hd) || n <= 0)
         return JB_EINVAL;
     int G = nh / nkv;
@@ -1275,7 +1321,7 @@ extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void
             return JB_ELAUNCH;                                                                 \
         launch(attn_tc_prefill_kernel<HDV>, dim3((unsigned)n_blocks * nkv), PF_THREADS,        \
                PrefillCfg<HDV>::SMEM_BYTES, st, mq, mk, mv, qblk, block_table, bt_stride,      \
-               (bf16 *)out, nh, nkv, G, R, window, scale);                                     \
+               (bf16 *)out, nh, nkv, G, R, window, scale, head_scale, sink);                   \
     } while (0)
     if (hd == 128)
         JB_PF(128);
@@ -1334,10 +1380,10 @@ static int attn_tc_decode(const void *q, const void *k_cache, const void *v_cach
     if (hd == 128)
         return launch_attn_rows<128>(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
                                      bt_stride, part, n, nh, nkv, window, scale, max_chunks,
-                                     chunks_per_cta, row0, n_rows, st);
+                                     chunks_per_cta, row0, n_rows, f.head_scale, st);
     return launch_attn_rows<64>(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
                                 bt_stride, part, n, nh, nkv, window, scale, max_chunks,
-                                chunks_per_cta, row0, n_rows, st);
+                                chunks_per_cta, row0, n_rows, f.head_scale, st);
 }
 
 extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void *v_cache,
@@ -1346,7 +1392,22 @@ extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void 
                                  int row0, int n_rows, int nh, int nkv, int hd, int window,
                                  float scale, int max_chunks, int chunks_per_cta, cudaStream_t st)
 {
+    return jb_attn_tc_decode_scaled(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
+                                    bt_stride, part, n, row0, n_rows, nh, nkv, hd, window, scale,
+                                    nullptr, max_chunks, chunks_per_cta, st);
+}
+
+// The same with a factor per head on the scores (float [nh], or null).
+extern "C" int jb_attn_tc_decode_scaled(const void *q, const void *k_cache, const void *v_cache,
+                                        long long n_pages, const int32_t *row_pos,
+                                        const int32_t *row_seq, const int32_t *block_table,
+                                        int bt_stride, float *part, int n, int row0, int n_rows,
+                                        int nh, int nkv, int hd, int window, float scale,
+                                        const float *head_scale, int max_chunks,
+                                        int chunks_per_cta, cudaStream_t st)
+{
     DecodeQkv f = {};
+    f.head_scale = head_scale;
     return attn_tc_decode(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table, bt_stride,
                           part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
                           chunks_per_cta, f, st);
@@ -1368,7 +1429,32 @@ extern "C" int jb_attn_tc_decode_qkv(const float *qkv, int S, long long split_st
                                      float scale, int max_chunks, int chunks_per_cta,
                                      cudaStream_t st)
 {
+    return jb_attn_tc_decode_qkv_bias(qkv, S, split_stride, nullptr, q_w, k_w, w_dt, eps, cs, sn,
+                                      k_cache, v_cache, append, n_pages, row_pos, row_seq,
+                                      block_table, bt_stride, part, n, row0, n_rows, nh, nkv, hd,
+                                      window, scale, nullptr, 0, max_chunks, chunks_per_cta, st);
+}
+
+// The same with the product's bias (float over the product's columns, or null)
+// added to the sums, a factor per head on the scores (float [nh], or null), and
+// rows of qkv that are ld floats apart (0: heads + 2 kv heads of hd values; a layer
+// that appends nothing may have q alone in its product).
+extern "C" int jb_attn_tc_decode_qkv_bias(const float *qkv, int S, long long split_stride,
+                                          const float *bias, const void *q_w, const void *k_w,
+                                          int w_dt, float eps, const float *cs, const float *sn,
+                                          void *k_cache, void *v_cache, int append,
+                                          long long n_pages, const int32_t *row_pos,
+                                          const int32_t *row_seq, const int32_t *block_table,
+                                          int bt_stride, float *part, int n, int row0, int n_rows,
+                                          int nh, int nkv, int hd, int window, float scale,
+                                          const float *head_scale, long long ld, int max_chunks,
+                                          int chunks_per_cta, cudaStream_t st)
+{
+    if (ld % 4 != 0 || (ld > 0 && ld < (long long)(append ? nh + 2 * nkv : nh) * hd))
+        return JB_EINVAL;
     auto aligned = [](const void *p, size_t to) { return (uintptr_t)p % to == 0; };
+    if (!aligned(bias, 16))
+        return JB_EINVAL;
     if (qkv == nullptr || S <= 0 || split_stride % 4 != 0 || !aligned(qkv, 16) ||
         (q_w == nullptr) != (k_w == nullptr) || (cs == nullptr) != (sn == nullptr) ||
         (w_dt != JB_F32 && w_dt != JB_BF16))
@@ -1377,7 +1463,8 @@ extern "C" int jb_attn_tc_decode_qkv(const float *qkv, int S, long long split_st
     if (!aligned(q_w, w_to) || !aligned(k_w, w_to) || !aligned(cs, 16) || !aligned(sn, 16))
         return JB_EINVAL;
     DecodeQkv f = {qkv, S, split_stride, q_w, k_w, w_dt == JB_F32, eps, cs, sn,
-                   append ? (bf16 *)k_cache : nullptr, append ? (bf16 *)v_cache : nullptr};
+                   append ? (bf16 *)k_cache : nullptr, append ? (bf16 *)v_cache : nullptr, bias,
+                   head_scale, ld};
     return attn_tc_decode(nullptr, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
                           bt_stride, part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
                           chunks_per_cta, f, st);

@@ -99,6 +99,25 @@ int jb_attn_tc_decode_qkv(const float *qkv, int S, long long split_stride, const
                           const int32_t *block_table, int bt_stride, float *part, int n, int row0,
                           int n_rows, int nh, int nkv, int hd, int window, float scale,
                           int max_chunks, int chunks_per_cta, cudaStream_t st);
+int jb_attn_tc_prefill_sink(const void *q, const void *k_cache, const void *v_cache,
+                            long long n_pages, const int32_t *qblk, int n_blocks,
+                            const int32_t *block_table, int bt_stride, void *out, int n, int nh,
+                            int nkv, int hd, int window, float scale, const float *head_scale,
+                            const float *sink, cudaStream_t st);
+int jb_attn_tc_decode_scaled(const void *q, const void *k_cache, const void *v_cache,
+                             long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
+                             const int32_t *block_table, int bt_stride, float *part, int n,
+                             int row0, int n_rows, int nh, int nkv, int hd, int window,
+                             float scale, const float *head_scale, int max_chunks,
+                             int chunks_per_cta, cudaStream_t st);
+int jb_attn_tc_decode_qkv_bias(const float *qkv, int S, long long split_stride, const float *bias,
+                               const void *q_w, const void *k_w, int w_dt, float eps,
+                               const float *cs, const float *sn, void *k_cache, void *v_cache,
+                               int append, long long n_pages, const int32_t *row_pos,
+                               const int32_t *row_seq, const int32_t *block_table, int bt_stride,
+                               float *part, int n, int row0, int n_rows, int nh, int nkv, int hd,
+                               int window, float scale, const float *head_scale, long long ld,
+                               int max_chunks, int chunks_per_cta, cudaStream_t st);
 int jb_attn_tc_error(void);
 long long jb_gemm_simt_scratch(int n, int m, int k);
 int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, float *out, int n, int m, int k,

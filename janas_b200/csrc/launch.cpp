@@ -299,12 +299,12 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
     int ni = as_int(n, "rows");
     int vd = g.value_dim();
     Buf out = d.pool.get((size_t)n * (size_t)g.nh * (size_t)vd * dtype_size(c.dt));
-    bool tc = !force_simt && g.plain() && c.dt == BF16 && (decode || blocks != nullptr) &&
-              attention_tc_ok(g.nh, g.nkv, g.hd);
+    bool tc = !force_simt && vd == g.hd && c.dt == BF16 && (decode || blocks != nullptr) &&
+              attention_tc_ok(g.nh, g.nkv, g.hd) && (decode || !g.head_scale || g.head_scale_positive);
     if (tc && !decode) {
-        check(jb_attn_tc_prefill(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
-                                 out.ptr, ni, g.nh, g.nkv, g.hd, g.window, g.scale, d.stream),
-              "attention (tcgen05, prefill)");
+        check(jb_attn_tc_prefill_sink(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
+                                      out.ptr, ni, g.nh, g.nkv, g.hd, g.window, g.scale, g.head_scale,
+                                      g.sink, d.stream), "attention (tcgen05, prefill)");
         return out;
     }
     int parts = max_chunks, per_cta = 1;
@@ -322,11 +322,12 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
     for (long long row0 = 0; row0 < n; row0 += rows_per_call) {
         int cnt = (int)std::min<long long>(rows_per_call, n - row0);
         if (tc) {
-            check(jb_attn_tc_decode(q, c.k, c.v, c.n_pages, row_pos, row_seq, c.block_table, c.bt_stride,
-                                    scratch.as<float>(), ni, (int)row0, cnt, g.nh, g.nkv, g.hd, g.window,
-                                    g.scale, max_chunks, per_cta, d.stream), "attention (tcgen05, decode)");
-            check(jb_attention_merge(scratch.as<float>(), row_pos, out.ptr, c.dt, (int)row0, cnt, g.nh, g.hd,
-                                     g.window, parts, per_cta, d.stream), "attention merge");
+            check(jb_attn_tc_decode_scaled(q, c.k, c.v, c.n_pages, row_pos, row_seq, c.block_table,
+                                           c.bt_stride, scratch.as<float>(), ni, (int)row0, cnt, g.nh, g.nkv,
+                                           g.hd, g.window, g.scale, g.head_scale, max_chunks, per_cta,
+                                           d.stream), "attention (tcgen05, decode)");
+            check(jb_attention_merge_sink(scratch.as<float>(), row_pos, out.ptr, c.dt, (int)row0, cnt, g.nh,
+                                          g.hd, g.window, parts, per_cta, g.sink, d.stream), "attention merge");
         } else {
             check(jb_attention_sink(q, c.k, c.v, c.dt, row_pos, row_seq, c.block_table, c.bt_stride,
                                     scratch.as<float>(), out.ptr, (int)row0, cnt, g.nh, g.nkv, g.hd, vd,
@@ -339,10 +340,12 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
 
 Buf attention_decode_qkv(Device &d, const Stack &qkv, const DevTensor *q_w, const DevTensor *k_w, float eps,
                          const float *cs, const float *sn, const AttnCache &c, const AttnGeometry &g,
-                         const int32_t *row_pos, const int32_t *row_seq, int max_chunks) {
-    if (c.dt != BF16 || !c.k || !jb_attn_tc_decode_runs(g.nh, g.nkv, g.hd)) return Buf();
-    long long width = (long long)(g.nh + 2 * g.nkv) * g.hd;
-    if (qkv.m != width) fail(JB_LLM_EINVAL, "attention: qkv is not heads + 2 kv_heads wide");
+                         const int32_t *row_pos, const int32_t *row_seq, int max_chunks, const float *bias) {
+    if (c.dt != BF16 || !c.k || !jb_attn_tc_decode_runs(g.nh, g.nkv, g.hd) || g.value_dim() != g.hd)
+        return Buf();
+    long long width = (long long)(g.nh + (c.writes ? 2 * g.nkv : 0)) * g.hd;
+    if (qkv.m != width && qkv.m != (long long)(g.nh + 2 * g.nkv) * g.hd)
+        fail(JB_LLM_EINVAL, "attention: qkv is not heads + 2 kv_heads wide");
     int w_dt = 0;
     if (q_w) {
         if (!k_w || q_w->dt != k_w->dt) fail(JB_LLM_EINVAL, "attention: q and k norm weights of one type");
@@ -360,15 +363,16 @@ Buf attention_decode_qkv(Device &d, const Stack &qkv, const DevTensor *q_w, cons
     Buf out = d.pool.get((size_t)n * (size_t)g.nh * (size_t)g.hd * 2);
     for (long long row0 = 0; row0 < n; row0 += rows_per_call) {
         int cnt = (int)std::min<long long>(rows_per_call, n - row0);
-        int code = jb_attn_tc_decode_qkv(qkv.data(), qkv.S, qkv.stride(), q_w ? q_w->ptr : nullptr,
-                                         k_w ? k_w->ptr : nullptr, w_dt, eps, cs, sn, c.k, c.v,
-                                         c.writes ? 1 : 0, c.n_pages, row_pos, row_seq, c.block_table,
-                                         c.bt_stride, scratch.as<float>(), ni, (int)row0, cnt, g.nh, g.nkv,
-                                         g.hd, g.window, g.scale, max_chunks, per_cta, d.stream);
+        int code = jb_attn_tc_decode_qkv_bias(qkv.data(), qkv.S, qkv.stride(), bias, q_w ? q_w->ptr : nullptr,
+                                              k_w ? k_w->ptr : nullptr, w_dt, eps, cs, sn, c.k, c.v,
+                                              c.writes ? 1 : 0, c.n_pages, row_pos, row_seq, c.block_table,
+                                              c.bt_stride, scratch.as<float>(), ni, (int)row0, cnt, g.nh,
+                                              g.nkv, g.hd, g.window, g.scale, g.head_scale, qkv.m, max_chunks,
+                                              per_cta, d.stream);
         if (code == -1 && row0 == 0) return Buf();      // an address the kernel's 16-byte loads cannot take
         check(code, "attention (tcgen05, decode, from the product's sums)");
-        check(jb_attention_merge(scratch.as<float>(), row_pos, out.ptr, BF16, (int)row0, cnt, g.nh, g.hd,
-                                 g.window, parts, per_cta, d.stream), "attention merge");
+        check(jb_attention_merge_sink(scratch.as<float>(), row_pos, out.ptr, BF16, (int)row0, cnt, g.nh, g.hd,
+                                      g.window, parts, per_cta, g.sink, d.stream), "attention merge");
     }
     return out;
 }

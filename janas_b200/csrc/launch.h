@@ -103,8 +103,8 @@ struct AttnGeometry {
     int vd = 0;                              // the values' head size; 0: as the keys'
     const float *head_scale = nullptr;       // float32 [nh] on the device: a factor per head on the scores
     const float *sink = nullptr;             // float32 [nh]: exp(sink) joins each softmax's denominator
+    bool head_scale_positive = true;         // every factor is > 0 (the prefill tensor-core kernel needs it)
     int value_dim() const { return vd > 0 ? vd : hd; }
-    bool plain() const { return !head_scale && !sink && value_dim() == hd; }
 };
 
 // what the attention kernels see of the cache and of the step's index arrays
@@ -154,10 +154,11 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
 
 // qk_norm_rope_append and attention(decode) in one kernel, from the q,k,v product's
 // partial sums; an empty Buf where the kernel does not take these sizes and types.
+// bias: float32 over the product's columns, added to its sums, or null.
 Buf attention_decode_qkv(Device &d, const Stack &qkv, const DevTensor *q_w, const DevTensor *k_w,
                          float eps, const float *cos, const float *sin, const AttnCache &c,
                          const AttnGeometry &g, const int32_t *row_pos, const int32_t *row_seq,
-                         int max_chunks);
+                         int max_chunks, const float *bias = nullptr);
 
 struct SamplerArrays {
     const int32_t *row_slot = nullptr;

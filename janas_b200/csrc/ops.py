@@ -278,6 +278,116 @@ def qk_norm_rope_append(qkv: torch.Tensor, q_weight: Optional[torch.Tensor],
 
 
 # ----------------------------------------------------------------- attention
+def embed_pos(table: torch.Tensor, pos_table: torch.Tensor, tokens: torch.Tensor,
+              row_pos: torch.Tensor) -> torch.Tensor:
+    """x[j] = table[tokens[j]] + pos_table[row_pos[j]] as float32 [n, dm]."""
+    _need(table, "table", _FLOATS, (None, None))
+    dm = table.shape[1]
+    _need(pos_table, "pos_table", _FLOATS, (None, dm))
+    n = tokens.shape[0]
+    _need(tokens, "tokens", torch.int32, (n,))
+    _need(row_pos, "row_pos", torch.int32, (n,))
+    x = torch.empty((n, dm), dtype=torch.float32, device=table.device)
+    _check(lib().jb_embed_pos(_p(table), _DT[table.dtype], _p(pos_table), _DT[pos_table.dtype],
+                              _p(tokens), _p(row_pos), _p(x), n, dm, _stream()), "embed_pos")
+    return x
+
+
+def dyt(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor,
+        out_dtype: torch.dtype, delta: Optional[torch.Tensor] = None,
+        rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dynamic Tanh: tanh(alpha x) weight + bias on the rows of x (float32 [n, dm]);
+    with ``delta`` (a stack of partial sums) x += sum(delta) first, in place; with
+    ``rows`` only those rows.  weight, bias [dm] and alpha [] or [1]: float32."""
+    _need(x, "x", torch.float32, (None, None))
+    n, dm = x.shape
+    _need(weight, "weight", torch.float32, (dm,))
+    _need(bias, "bias", torch.float32, (dm,))
+    _need(alpha, "alpha", torch.float32)
+    S, stride = 0, 0
+    if delta is not None:
+        delta = stack(delta)
+        _need(delta, "delta", torch.float32, (None, n, dm))
+        S, stride = delta.shape[0], n * dm
+    n_out = n
+    if rows is not None:
+        _need(rows, "rows", torch.int32, (None,))
+        n_out = rows.shape[0]
+    out = torch.empty((n_out, dm), dtype=out_dtype, device=x.device)
+    _check(lib().jb_dyt(_p(x), _p(delta), S, stride, _p(rows), _p(weight), _p(bias), _p(alpha),
+                        _p(out), _DT[out_dtype], n_out, dm, _stream()), "dyt")
+    return out
+
+
+def gate_mul(y: torch.Tensor, y_bias: Optional[torch.Tensor], g: torch.Tensor,
+             g_bias: Optional[torch.Tensor], g_col0: int = 0) -> torch.Tensor:
+    """(sum y + y_bias) * sigmoid(sum g + g_bias) as float32 [n, dm]; y, g: stacks of
+    partial sums; g's rows may be wider than dm (the gate starts at column g_col0)."""
+    y, g = stack(y), stack(g)
+    _need(y, "y", torch.float32, (None, None, None))
+    Sy, n, dm = y.shape
+    _need(g, "g", torch.float32, (None, n, None))
+    out = torch.empty((n, dm), dtype=torch.float32, device=y.device)
+    _check(lib().jb_gate_mul(_p(y), Sy, n * dm, _p(y_bias), _p(g), g.shape[0], n * g.shape[2],
+                             g.shape[2], g_col0, _p(g_bias), _p(out), n, dm, _stream()), "gate_mul")
+    return out
+
+
+def gated_dyt_residual(x: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor],
+                       g: torch.Tensor, g_bias: Optional[torch.Tensor], post, nxt=None,
+                       out_dtype: torch.dtype = torch.float32) -> Optional[torch.Tensor]:
+    """x += dyt_post(gate_mul(y, g)) in place; with ``nxt`` also returns dyt_nxt(x).
+    post, nxt: (weight, bias, alpha) float32 tensors."""
+    y, g = stack(y), stack(g)
+    _need(x, "x", torch.float32, (None, None))
+    n, dm = x.shape
+    _need(y, "y", torch.float32, (None, n, dm))
+    _need(g, "g", torch.float32, (None, n, None))
+    out = torch.empty((n, dm), dtype=out_dtype, device=x.device) if nxt is not None else None
+    nw, nb, na = nxt if nxt is not None else (None, None, None)
+    _check(lib().jb_gated_dyt_residual(_p(x), _p(y), y.shape[0], n * dm, _p(y_bias), _p(g),
+                                       g.shape[0], n * g.shape[2], g.shape[2], 0, _p(g_bias),
+                                       _p(post[0]), _p(post[1]), _p(post[2]), _p(nw), _p(nb),
+                                       _p(na), _p(out), _DT[out_dtype], n, dm, _stream()),
+           "gated_dyt_residual")
+    return out
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float,
+             out_dtype: torch.dtype) -> torch.Tensor:
+    """c0 n(z) + c1 n(z^2) + c2 n(z^3) + c3 per row, n(u) = u / sqrt(mean(u^2) + eps);
+    z: a stack of partial sums [S, n, ff]; coef: float32 [4]."""
+    z = stack(z)
+    _need(z, "z", torch.float32, (None, None, None))
+    S, n, ff = z.shape
+    _need(coef, "coef", torch.float32, (4,))
+    out = torch.empty((n, ff), dtype=out_dtype, device=z.device)
+    _check(lib().jb_polynorm(_p(z), S, n * ff, ff, _p(coef), float(eps), _p(out), _DT[out_dtype],
+                             n, ff, _stream()), "polynorm")
+    return out
+
+
+def qkv_bias_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], row_pos: torch.Tensor,
+                    row_seq: torch.Tensor, block_table: torch.Tensor,
+                    k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                    num_heads: int, head_dim: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """The fused [q | k | v] product's sums plus its bias: returns q [n, heads, hd] in
+    out_dtype and writes K and V to the cache pages at the rows' positions; with no
+    caches the product holds q alone."""
+    qkv = stack(qkv)
+    _need(qkv, "qkv", torch.float32, (None, None, None))
+    S, n, width = qkv.shape
+    append = k_cache is not None
+    nkv = k_cache.shape[1] if append else 0
+    vd = v_cache.shape[3] if append else 0
+    q = torch.empty((n, num_heads, head_dim), dtype=out_dtype, device=qkv.device)
+    _check(lib().jb_qkv_bias_append(_p(qkv), S, n * width, width, _p(bias), _p(row_pos), _p(row_seq),
+                                    _p(block_table), block_table.shape[1], _p(q), _p(k_cache),
+                                    _p(v_cache), _DT[out_dtype], n, num_heads, nkv, head_dim, vd,
+                                    1 if append else 0, _stream()), "qkv_bias_append")
+    return q
+
+
 def attention_chunk() -> int:
     return int(lib().jb_attention_chunk())
 
@@ -316,7 +426,9 @@ def attention_blocks(seq_row0, seq_pos0, seq_len, positions_per_block: int,
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               row_pos: torch.Tensor, row_seq: torch.Tensor, block_table: torch.Tensor,
               window: int, scale: float, max_chunks: int, blocks: Optional[torch.Tensor] = None,
-              decode: bool = False, force_simt: bool = False) -> torch.Tensor:
+              decode: bool = False, force_simt: bool = False,
+              head_scale: Optional[torch.Tensor] = None,
+              sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal GQA attention of every row over its sequence's cache pages.
 
     q: [n, heads, hd]; caches [pages, kv_heads, PAGE, hd] of q's dtype.  Row r
@@ -329,26 +441,38 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     says how the rows are arranged: ``decode=True`` (every row is the one new
     token of its sequence) or ``blocks`` (from ``attention_blocks``: runs of
     consecutive positions of one sequence).  Everything else, and float32, runs on
-    the plain kernel."""
+    the plain kernel.
+
+    The values may have a head size of their own (v_cache [pages, kv_heads, PAGE,
+    vd]; the result is then [n, heads, vd]).  ``head_scale`` (float32 [heads]) is a
+    factor per head on the scores; ``sink`` (float32 [heads]) adds exp(sink) once to
+    each softmax's denominator, with no value."""
     _need(q, "q", _FLOATS, (None, None, None))
     n, nh, hd = q.shape
     _need(k_cache, "k_cache", q.dtype, (None, None, PAGE, hd))
-    _need(v_cache, "v_cache", q.dtype, tuple(k_cache.shape))
     nkv = k_cache.shape[1]
+    _need(v_cache, "v_cache", q.dtype, (k_cache.shape[0], nkv, PAGE, None))
+    vd = v_cache.shape[3]
+    if head_scale is not None:
+        _need(head_scale, "head_scale", torch.float32, (nh,))
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (nh,))
     _need(row_pos, "row_pos", torch.int32, (n,))
     _need(row_seq, "row_seq", torch.int32, (n,))
     _need(block_table, "block_table", torch.int32, (None, None))
-    out = torch.empty_like(q)
+    out = torch.empty((n, nh, vd), dtype=q.dtype, device=q.device)
     L = lib()
-    tc = (not force_simt and q.dtype == torch.bfloat16 and (decode or blocks is not None)
-          and bool(L.jb_attn_tc_ok(nh, nkv, hd)))
+    tc = (not force_simt and vd == hd and q.dtype == torch.bfloat16
+          and (decode or blocks is not None) and bool(L.jb_attn_tc_ok(nh, nkv, hd))
+          and (decode or head_scale is None or bool((head_scale > 0).all())))
     if tc and not decode:
         _need(blocks, "blocks", torch.int32, (None, 4))
-        _check(L.jb_attn_tc_prefill(_p(q), _p(k_cache), _p(v_cache),
-                                    int(k_cache.shape[0]), _p(blocks),
-                                    blocks.shape[0], _p(block_table), block_table.shape[1],
-                                    _p(out), n, nh, nkv, hd, window, float(scale),
-                                    _stream()), "attention (tcgen05, prefill)")
+        _check(L.jb_attn_tc_prefill_sink(_p(q), _p(k_cache), _p(v_cache),
+                                         int(k_cache.shape[0]), _p(blocks),
+                                         blocks.shape[0], _p(block_table), block_table.shape[1],
+                                         _p(out), n, nh, nkv, hd, window, float(scale),
+                                         _p(head_scale), _p(sink), _stream()),
+               "attention (tcgen05, prefill)")
         return out
     if tc:
         # CTAs per (token, KV head): each runs over per_cta chunks and leaves one partial
@@ -360,26 +484,28 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         parts = (max_chunks + per_cta - 1) // per_cta
     else:
         parts, per_cta = max_chunks, 1
-    per_row = int(L.jb_attention_scratch(1, nh, hd, parts))
+    per_row = int(L.jb_attention_scratch(1, nh, vd, parts))
     rows_per_call = max(1, min(n, (_ATT_SCRATCH_BYTES // 4) // max(per_row, 1)))
     scratch = _scratch(q.device, per_row * rows_per_call)
     for row0 in range(0, n, rows_per_call):
         cnt = min(rows_per_call, n - row0)
         if tc:
-            _check(L.jb_attn_tc_decode(_p(q), _p(k_cache), _p(v_cache),
-                                       int(k_cache.shape[0]), _p(row_pos),
-                                       _p(row_seq), _p(block_table), block_table.shape[1],
-                                       _p(scratch), n, row0, cnt, nh, nkv, hd, window,
-                                       float(scale), max_chunks, per_cta, _stream()),
+            _check(L.jb_attn_tc_decode_scaled(_p(q), _p(k_cache), _p(v_cache),
+                                              int(k_cache.shape[0]), _p(row_pos),
+                                              _p(row_seq), _p(block_table), block_table.shape[1],
+                                              _p(scratch), n, row0, cnt, nh, nkv, hd, window,
+                                              float(scale), _p(head_scale), max_chunks, per_cta,
+                                              _stream()),
                    "attention (tcgen05, decode)")
-            _check(L.jb_attention_merge(_p(scratch), _p(row_pos), _p(out), _DT[q.dtype], row0, cnt,
-                                        nh, hd, window, parts, per_cta, _stream()),
-                   "attention merge")
+            _check(L.jb_attention_merge_sink(_p(scratch), _p(row_pos), _p(out), _DT[q.dtype], row0,
+                                             cnt, nh, hd, window, parts, per_cta, _p(sink),
+                                             _stream()), "attention merge")
         else:
-            _check(L.jb_attention(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
-                                  _p(row_seq), _p(block_table), block_table.shape[1], _p(scratch),
-                                  _p(out), row0, cnt, nh, nkv, hd, window, float(scale),
-                                  max_chunks, _stream()), "attention", kernels=2)
+            _check(L.jb_attention_sink(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
+                                       _p(row_seq), _p(block_table), block_table.shape[1],
+                                       _p(scratch), _p(out), row0, cnt, nh, nkv, hd, vd, window,
+                                       float(scale), _p(head_scale), _p(sink), max_chunks,
+                                       _stream()), "attention", kernels=2)
     return out
 
 

@@ -251,6 +251,14 @@ public:
         if (bias_) b_o_ = take(t, name(p, n_o_ + n_bias_));
         g_.head_scale = head_scale_ ? (const float *)temp_.ptr : nullptr;
         g_.sink = sink_ ? (const float *)sinks_.ptr : nullptr;
+        if (head_scale_) {
+            // one kernel takes the largest raw score before the factor: it needs factors > 0
+            std::vector<float> host((size_t)g_.nh);
+            cuda_check(cudaMemcpy(host.data(), temp_.ptr, host.size() * 4, cudaMemcpyDeviceToHost),
+                       "reading the heads' factors");
+            g_.head_scale_positive = true;
+            for (float v : host) g_.head_scale_positive = g_.head_scale_positive && v > 0.0f;
+        }
     }
 
     size_t weight_bytes() const override {
@@ -277,13 +285,20 @@ public:
                                         : "sink_attention: a layer without key and value products needs "
                                           "another layer's cache (cache_of in the run order)");
         long long n = ctx.n_rows;
+        const float *b_in = bias_ ? (const float *)b_in_.ptr : nullptr;
         Stack qkv = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
-        Buf q = ops::qkv_bias_append(d, qkv, bias_ ? (const float *)b_in_.ptr : nullptr, ctx.row_pos, ctx.row_seq,
-                                     cache.kv, g_, ctx.dtype, own_kv_);
-        qkv.buf.reset();
         int max_chunks = (int)(ctx.max_pos / chunk_ + 1);
         if (g_.window) max_chunks = std::min(max_chunks, (g_.window - 1) / chunk_ + 2);
         bool decode = ctx.kind == DECODE;
+        if (decode && ctx.dtype == BF16) {
+            // one new token per sequence: the attention kernel makes q and the new key and
+            // value from the product's sums and its bias itself, where it takes the sizes
+            Buf a = ops::attention_decode_qkv(d, qkv, nullptr, nullptr, 0.0f, nullptr, nullptr, cache.kv, g_,
+                                              ctx.row_pos, ctx.row_seq, max_chunks, b_in);
+            if (a) return output(ctx, a);
+        }
+        Buf q = ops::qkv_bias_append(d, qkv, b_in, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype, own_kv_);
+        qkv.buf.reset();
         const int32_t *blocks = nullptr;
         int n_blocks = 0;
         if (!decode && ctx.dtype == BF16 && ops::attention_tc_ok(g_.nh, g_.nkv, g_.hd) && g_.vd == g_.hd &&
@@ -302,7 +317,11 @@ public:
         }
         Buf a = ops::attention(d, q.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, blocks, n_blocks,
                                decode);
-        Stack out = ops::linear(d, a.ptr, ctx.dtype, n, (long long)g_.nh * g_.vd, w_o_);
+        return output(ctx, a);
+    }
+
+    Stack output(StepContext &ctx, const Buf &a) {
+        Stack out = ops::linear(*ctx.dev, a.ptr, ctx.dtype, ctx.n_rows, (long long)g_.nh * g_.vd, w_o_);
         out.bias = bias_ ? (const float *)b_o_.ptr : nullptr;
         return out;
     }

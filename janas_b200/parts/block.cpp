@@ -30,7 +30,8 @@ public:
 
 // block_params: hidden_size; mixer_gate / ffn_gate: the tensor names (below the
 // layer's prefix) of the gates' matrices [hidden, hidden], absent or null for no
-// gate; gate_bias: the suffix of a gate's bias vector ("" for none).
+// gate; gate_bias: the suffix of a gate's bias vector ("" for none); fuse (default
+// true): false runs gate, norm and add as kernels of their own.
 class SandwichBlock : public Block {
 public:
     SandwichBlock(BlockParts p, const LayerSpec &ls, DType dt, Device *d) : Block(std::move(p)), dev_(d) {
@@ -41,6 +42,7 @@ public:
         if (bp.get("mixer_gate").is_string()) gate_name_[0] = bp.get("mixer_gate").as_string();
         if (bp.get("ffn_gate").is_string() && feed_forward) gate_name_[1] = bp.get("ffn_gate").as_string();
         if (bp.get("gate_bias").is_string()) bias_suffix_ = bp.get("gate_bias").as_string();
+        if (bp.get("fuse").is_bool()) fuse_ = bp.get("fuse").as_bool();
         // tensors of an absent feed-forward's surroundings that a file may still
         // hold: tolerated and not read
         if (!feed_forward)
@@ -123,7 +125,7 @@ private:
         long long n = ctx.n_rows;
         const float *g_bias = gate_bias_[which] ? (const float *)gate_bias_[which].ptr : nullptr;
         ops::DytParams pp, np;
-        if (g && post->dynamic_tanh(&pp)) {
+        if (fuse_ && g && post->dynamic_tanh(&pp)) {
             bool fuse_next = next && next->dynamic_tanh(&np);
             Buf out = ops::gated_dyt_residual(d, x, y, g, 0, g_bias, pp, fuse_next ? &np : nullptr, ctx.dtype);
             if (fuse_next) {
@@ -151,6 +153,7 @@ private:
 
     Device *dev_;
     long long hidden_ = 0;
+    bool fuse_ = true;      // false: every step as a kernel of its own (for comparisons)
     std::string gate_name_[2], bias_suffix_;
     DevTensor gate_[2], gate_bias_[2];
     std::vector<std::pair<std::string, std::vector<long long>>> unused_;

@@ -52,9 +52,9 @@ def gate(h: torch.Tensor, W: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def sink_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, temp: torch.Tensor,
-                   sink: torch.Tensor, pos0: int = 0) -> torch.Tensor:
+                   sink: torch.Tensor, pos0: int = 0, window: int = 0) -> torch.Tensor:
     """q [T, H, D], k [S, G, D], v [S, G, Dv]; row i of q sits at position pos0 + i and sees
-    keys 0 .. pos0 + i.  Returns [T, H, Dv]."""
+    keys 0 .. pos0 + i (with a window w, only the last w of them).  Returns [T, H, Dv]."""
     T, H, D = q.shape
     S, G, Dv = v.shape
     out = torch.zeros(T, H, Dv)
@@ -64,6 +64,8 @@ def sink_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: flo
         i = torch.arange(T).unsqueeze(1) + pos0
         j = torch.arange(S).unsqueeze(0)
         s = s.masked_fill(j > i, -math.inf)
+        if window > 0:
+            s = s.masked_fill(j < i + 1 - window, -math.inf)
         m = torch.maximum(s.max(dim=1, keepdim=True).values, sink[a].reshape(1, 1))
         e = torch.exp(s - m)
         den = e.sum(dim=1, keepdim=True) + torch.exp(sink[a] - m)
