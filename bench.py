@@ -7,6 +7,7 @@
     python bench.py --impl reference ...     (the reference's own bench program, on the CPU)
     python bench.py --only decode|prefill|timeline ...   (one part, for profiling)
     python bench.py --only generate [--model 8b] ...      (unequal prompts, then 256 tokens each)
+    python bench.py --only zuzelorn [--layers 8]           (the Zuzelorn design beside Qwen3 at equal sizes)
 
 The default run has the layer sizes of Qwen3-4B (36 layers, hidden 2560, 32
 heads, 8 KV heads, head size 128, feed-forward 9728, vocabulary 151936, tied
@@ -370,6 +371,136 @@ def generate_workload(eng, args, rng, new_tokens=256, runs=3):
     return out
 
 
+# ---- the Zuzelorn design beside the Qwen3 decoder at equal sizes
+# width, heads, KV heads, head size, feed-forward width: layer sizes of real models
+DESIGN_SIZES = {
+    "1b": (2048, 16, 8, 128, 6144),
+    "4b": (2560, 32, 8, 128, 9728),
+    "8b": (4096, 32, 8, 128, 12288),
+    "4b-heads64": (2560, 32, 8, 64, 9728),
+}
+
+
+def zuzelorn_cfg(size, n_layers, vocab, max_positions, share=0):
+    """A Zuzelorn config.json of the given layer sizes.  share: every layer whose
+    number is no multiple of ``share`` reads the keys and values of the last
+    multiple before it (0: every layer has its own)."""
+    dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
+    layers = []
+    for i in range(n_layers):
+        m = {"dim": hd, "heads": nh, "kv_heads": nkv, "scale": hd ** -0.5, "vdim": hd}
+        if share and i % share:
+            m["kv_from"] = i - i % share
+        layers.append({"type": "attention", "mixer": m, "mlp": {"ff": ff, "kind": "dense"}})
+    return {"architecture": "Zuzelorn", "layers": layers, "logit_scale": 1.0,
+            "max_positions": max_positions, "norm": {"eps": 1e-5}, "vocab": vocab, "width": dm}
+
+
+def qwen3_cfg(size, n_layers, vocab, max_positions):
+    dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
+    return dict(QWEN3_4B, num_hidden_layers=n_layers, hidden_size=dm, num_attention_heads=nh,
+                num_key_value_heads=nkv, head_dim=hd, intermediate_size=ff, vocab_size=vocab,
+                tie_word_embeddings=False, max_position_embeddings=max_positions)
+
+
+def design_flops(design, size, n_layers, tokens, vocab):
+    """Multiply-adds times two of one prompt: the layers' products (Qwen3: q, k, v, o
+    and three feed-forward matrices; Zuzelorn: q, k, v, o, two feed-forward matrices
+    and two gates of width x width), the causal attention, the head for one row."""
+    dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
+    qd, kvd = nh * hd, nkv * hd
+    mats = dm * (qd + 2 * kvd) + qd * dm + (3 * dm * ff if design == "qwen3" else 2 * dm * ff + 2 * dm * dm)
+    attn = 4 * qd * tokens * (tokens + 1) / 2
+    return n_layers * (2 * mats * tokens + attn) + 2 * dm * vocab
+
+
+def kernel_table(events):
+    """name -> (launches, microseconds on the critical path, sum of durations)."""
+    events.sort(key=lambda e: e.time_range.start)
+    prev_end = events[0].time_range.start
+    per = {}
+    for e in events:
+        gain = max(0.0, e.time_range.end - prev_end)
+        name = e.name.split("(")[0].split("<")[0].replace("void ", "").replace("jb::", "")[:40]
+        c = per.setdefault(name, [0, 0.0, 0.0])
+        c[0] += 1
+        c[1] += gain
+        c[2] += e.time_range.end - e.time_range.start
+        prev_end = max(prev_end, e.time_range.end)
+    return per
+
+
+def profile_kernels(fn):
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        fn()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+           and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()]
+    return kernel_table(evs)
+
+
+def design_compare(args):
+    """Prefill and decode throughput of a Zuzelorn model and of a Qwen3 model of the
+    same layer sizes, layer count, vocabulary and random weights, with each kernel's
+    time in one prefill step and one decode step.  One JSON line per size and design."""
+    import numpy as np
+    from janas_b200.engine import Engine, StepEntry
+    pk = peaks()
+    n_layers = args.layers if args.layers > 0 else 8
+    vocab, T, batch, context = 32768, args.prefill_tokens, args.batch, args.context
+    max_positions = (max(T, context) + 1024 + 1023) // 1024 * 1024
+    room = (context + 2 * (args.warmup + args.steps + 16) + 63) // 64 * 64
+    sizes = [args.design_size] if args.design_size else ["1b", "4b", "8b"]
+    for size in sizes:
+        designs = [("qwen3", qwen3_cfg(size, n_layers, vocab, max_positions)),
+                   ("zuzelorn", zuzelorn_cfg(size, n_layers, vocab, max_positions))]
+        if args.share:
+            designs.append((f"zuzelorn-share{args.share}",
+                            zuzelorn_cfg(size, n_layers, vocab, max_positions, args.share)))
+        for design, cfg in designs:
+            rng = np.random.default_rng(0)
+            eng = Engine.open_random(cfg, seed=0, dtype=args.dtype, max_tokens=max(room * batch, T + 64),
+                                     max_seqs=batch, n_ctx=max_positions)
+            pre_ms = prefill_timed(eng, rng, T)
+            flops = design_flops(design.split("-")[0], size, n_layers, T, vocab)
+
+            def one_prefill():
+                s = eng.new_sequence()
+                eng.step([StepEntry(s, rng.integers(0, vocab, size=T).tolist(), [T - 1])])
+                eng.free_sequence(s)
+            pre_kernels = profile_kernels(one_prefill)
+            slots, toks = fill(eng, batch, context, rng)
+            ms, n_launch, toks = decode_device_timed(eng, slots, toks, args.steps, args.warmup)
+            nbytes = step_bytes(eng, batch, context + args.warmup + args.steps // 2)
+            state = {"toks": toks}
+
+            def three_steps():
+                state["toks"] = drive(eng, slots, state["toks"], 3)
+            dec_kernels = profile_kernels(three_steps)
+            eng.check()
+            line = {"design": design, "size": size, "layers": n_layers, "dtype": args.dtype,
+                    "weight_bytes": eng.info()["weight_bytes"],
+                    "prefill": {"tokens": T, "ms": round(pre_ms, 3), "tokens_per_s": round(T / pre_ms * 1e3),
+                                "tflops": round(flops / pre_ms / 1e9, 1),
+                                "frac_of_measured": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3)},
+                    "decode": {"batch": batch, "context": context, "ms_per_step": round(ms, 4),
+                               "tokens_per_s": round(batch / ms * 1e3), "kernels_per_step": n_launch // args.steps,
+                               "gb_per_step": round(nbytes / 1e9, 3),
+                               "frac_of_measured": round(nbytes / (ms / 1e3) / (pk["hbm_gbs"] * 1e9), 3)},
+                    "prefill_kernels_us": {k: [v[0], round(v[1], 1), round(v[2], 1)]
+                                           for k, v in sorted(pre_kernels.items(), key=lambda kv: -kv[1][1])},
+                    "decode_kernels_us_per_step": {k: [v[0] // 3, round(v[1] / 3, 2), round(v[2] / 3, 2)]
+                                                   for k, v in sorted(dec_kernels.items(),
+                                                                      key=lambda kv: -kv[1][1])}}
+            print(json.dumps(line), flush=True)
+            eng.close()
+            del eng
+    return 0
+
+
 def other_config(model, extra):
     """Runs this program for another model size in a process of its own (its
     weights and cache are given back when it ends); returns its JSON line."""
@@ -398,13 +529,20 @@ def main():
                     help="skip decoding at batch 1 and 64 and the 32-bit points")
     ap.add_argument("--all-configs", action="store_true",
                     help="also the 8B workload (unequal prompts, 256 steps) and the 32B points")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "prefill-timeline", "generate"],
+    ap.add_argument("--design-size", default="", choices=[""] + sorted(DESIGN_SIZES),
+                    help="--only zuzelorn: one of the layer sizes (default: 1b, 4b and 8b)")
+    ap.add_argument("--share", type=int, default=0,
+                    help="--only zuzelorn: also a model whose layers share keys and values in groups of this many")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "prefill-timeline", "generate",
+                                                    "zuzelorn"],
                     help="run one part only and print its time (for profiling; no JSON line "
                          "but for generate); prefill-timeline: each kernel's share of one prefill "
                          "step; timeline: when each kernel of one replayed decode "
                          "step ends; generate: --batch prompts of lengths uniform in [64, "
                          "--context], all in one step, then 256 tokens each through the Python "
-                         "entry point")
+                         "entry point; zuzelorn: prefill and decoding of a Zuzelorn model beside a "
+                         "Qwen3 model of equal layer sizes (--layers, default 8), with every "
+                         "kernel's time")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -412,6 +550,9 @@ def main():
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
+    if args.only == "zuzelorn":
+        args.warmup = max(args.warmup, 3)
+        return design_compare(args)
     full_layers = MODELS[args.model]["num_hidden_layers"]
     if args.layers <= 0:
         args.layers = full_layers
