@@ -416,6 +416,8 @@ def design_flops(design, size, n_layers, tokens, vocab):
 
 def kernel_table(events):
     """name -> (launches, microseconds on the critical path, sum of durations)."""
+    if not events:          # no activity records (another profiler holds them)
+        return {}
     events.sort(key=lambda e: e.time_range.start)
     prev_end = events[0].time_range.start
     per = {}

@@ -39,6 +39,56 @@ __device__ __forceinline__ float dyt1(float v, float alpha, float w, float b)
 
 __device__ __forceinline__ float sigmoid1(float v) { return 1.0f / (1.0f + expf(-v)); }
 
+// The same two with the hardware's exponential and reciprocal, for the bfloat16
+// path: absolute error of a few 1e-7 (tanh(t) = 1 - 2 / (1 + e^(2t))), far below
+// what that path's stored activations round to.  FAST false: the library functions.
+template <bool FAST> __device__ __forceinline__ float tanh_f(float t)
+{
+    if (!FAST)
+        return tanhf(t);
+    float e = __expf(2.0f * fminf(t, 40.0f));
+    return 1.0f - __fdividef(2.0f, 1.0f + e);
+}
+template <bool FAST> __device__ __forceinline__ float dyt_f(float v, float alpha, float w, float b)
+{
+    return fmaf(tanh_f<FAST>(alpha * v), w, b);
+}
+template <bool FAST> __device__ __forceinline__ float sigmoid_f(float v)
+{
+    if (!FAST)
+        return 1.0f / (1.0f + expf(-v));
+    return __fdividef(1.0f, 1.0f + __expf(-fmaxf(v, -80.0f)));
+}
+
+// Four neighbouring columns' sums of S partial sums, added in the order 0 .. S-1
+// (the same order as add_partials), eight partial sums fetched together.
+__device__ __forceinline__ float4 sum_partials4(const float *__restrict__ p, int S, size_t stride)
+{
+    // one partial sum (every product of many rows): nothing to add, and no loop whose
+    // bookkeeping would cost more than the kernels around it do
+    if (S == 1)
+        return load4(p);
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s0 = 0; s0 < S; s0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (s0 + u < S)
+                t[u] = load4(p + (size_t)(s0 + u) * stride);
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (s0 + u < S) {
+                v.x += t[u].x; v.y += t[u].y; v.z += t[u].z; v.w += t[u].w;
+            }
+    }
+    return v;
+}
+
+__device__ __forceinline__ float4 add4(float4 a, float4 b)
+{
+    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+
 // x: [n, dm] float, updated in place when delta is given (x += sum of delta's S
 // partial sums).  row_idx (or null) picks the rows that are normed; out has one
 // row per picked row.  One thread per value.
@@ -120,6 +170,176 @@ __global__ void gated_dyt_residual_kernel(
     x[i] = v;
     if (out != nullptr)
         out[i] = from_f<TO>(dyt1(v, na, nwv, nbv));
+}
+
+// The same with four neighbouring columns per thread (dm, the gate's row length and
+// first column multiples of 4, everything at 16-byte boundaries).
+// Grid: x over rows, y over blocks of columns (no division per thread).
+template <typename TO, bool FAST>
+__global__ void __launch_bounds__(256)
+gated_dyt_residual_vec_kernel(
+    float *__restrict__ x, const float *__restrict__ y, int Sy, size_t y_stride,
+    const float *__restrict__ y_bias, const float *__restrict__ g, int Sg, size_t g_stride,
+    int g_ld, int g_col0, const float *__restrict__ g_bias, const float *__restrict__ pw,
+    const float *__restrict__ pb, const float *__restrict__ palpha, const float *__restrict__ nw,
+    const float *__restrict__ nb, const float *__restrict__ nalpha, TO *__restrict__ out, int dm)
+{
+    pdl_trigger();
+    size_t row = blockIdx.x;
+    int c = (int)(blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= dm)
+        return;
+    size_t i = row * dm + c;
+    float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 yb = y_bias ? load4(y_bias + c) : zero, gb = g_bias ? load4(g_bias + c) : zero;
+    float4 pwv = load4(pw + c), pbv = load4(pb + c);
+    float pa = palpha[0];
+    float4 nwv = zero, nbv = zero;
+    float na = 0.0f;
+    if (out != nullptr) {
+        nwv = load4(nw + c);
+        nbv = load4(nb + c);
+        na = nalpha[0];
+    }
+    pdl_wait();
+    float4 xv = load4(x + i);
+    float4 yv = add4(sum_partials4(y + i, Sy, y_stride), yb);
+    float4 gv = add4(sum_partials4(g + row * g_ld + g_col0 + c, Sg, g_stride), gb);
+    xv.x += dyt_f<FAST>(yv.x * sigmoid_f<FAST>(gv.x), pa, pwv.x, pbv.x);
+    xv.y += dyt_f<FAST>(yv.y * sigmoid_f<FAST>(gv.y), pa, pwv.y, pbv.y);
+    xv.z += dyt_f<FAST>(yv.z * sigmoid_f<FAST>(gv.z), pa, pwv.z, pbv.z);
+    xv.w += dyt_f<FAST>(yv.w * sigmoid_f<FAST>(gv.w), pa, pwv.w, pbv.w);
+    store4(x + i, xv);
+    if (out != nullptr)
+        store4(out + i, make_float4(dyt_f<FAST>(xv.x, na, nwv.x, nbv.x), dyt_f<FAST>(xv.y, na, nwv.y, nbv.y),
+                                    dyt_f<FAST>(xv.z, na, nwv.z, nbv.z), dyt_f<FAST>(xv.w, na, nwv.w, nbv.w)));
+}
+
+__device__ __forceinline__ void power_sums(float4 v, float &s2, float &s4, float &s6)
+{
+    float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        float v2 = e[k] * e[k], v3 = v2 * e[k];
+        s2 += v2;
+        s4 = fmaf(v2, v2, s4);
+        s6 = fmaf(v3, v3, s6);
+    }
+}
+
+__device__ __forceinline__ float4 poly4(float4 v, float c0, float c1, float c2, float c3, float r1,
+                                        float r2, float r3)
+{
+    float e[4] = {v.x, v.y, v.z, v.w}, o[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        float v2 = e[k] * e[k];
+        o[k] = c0 * (e[k] * r1) + c1 * (v2 * r2) + c2 * (v2 * e[k] * r3) + c3;
+    }
+    return make_float4(o[0], o[1], o[2], o[3]);
+}
+
+// Three sums over a block at once; every thread gets them.  red: 96 floats.
+__device__ __forceinline__ void block_sum3(float &a, float &b, float &c, float *red)
+{
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int nwarp = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    c = warp_sum(c);
+    __syncthreads();
+    if (lane == 0) {
+        red[warp] = a;
+        red[32 + warp] = b;
+        red[64 + warp] = c;
+    }
+    __syncthreads();
+    a = warp_sum(lane < nwarp ? red[lane] : 0.0f);
+    b = warp_sum(lane < nwarp ? red[32 + lane] : 0.0f);
+    c = warp_sum(lane < nwarp ? red[64 + lane] : 0.0f);
+}
+
+// PolyNorm with the row held in registers: a block of up to 512 threads per row,
+// KEEP groups of four neighbouring values per thread (ff a multiple of 4, up to
+// 16,384), one pass over memory, two blocks to an SM.  The sums run in an order
+// that depends on ff alone.
+template <typename TO, int KEEP>
+__global__ void __launch_bounds__(512, 2)
+polynorm_vec_kernel(const float *__restrict__ z, int S, size_t stride, int z_ld,
+                    const float *__restrict__ coef, float eps, TO *__restrict__ out, int ff)
+{
+    __shared__ float red[96];
+    pdl_trigger();
+    float c0 = coef[0], c1 = coef[1], c2 = coef[2], c3 = coef[3];
+    pdl_wait();
+    size_t row = blockIdx.x;
+    const float *zr = z + row * z_ld;
+    int nv = ff / 4;
+    float4 v[KEEP];
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+#pragma unroll
+    for (int u = 0; u < KEEP; u++) {
+        int j = threadIdx.x + u * blockDim.x;
+        v[u] = j < nv ? sum_partials4(zr + 4 * j, S, stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        power_sums(v[u], s2, s4, s6);
+    }
+    block_sum3(s2, s4, s6, red);
+    float r1 = 1.0f / sqrtf(s2 / (float)ff + eps);
+    float r2 = 1.0f / sqrtf(s4 / (float)ff + eps);
+    float r3 = 1.0f / sqrtf(s6 / (float)ff + eps);
+    TO *o = out + row * ff;
+#pragma unroll
+    for (int u = 0; u < KEEP; u++) {
+        int j = threadIdx.x + u * blockDim.x;
+        if (j < nv)
+            store4(o + 4 * j, poly4(v[u], c0, c1, c2, c3, r1, r2, r3));
+    }
+}
+
+// PolyNorm for few rows, bfloat16 out: a row is shared out among the C CTAs of a
+// cluster (per4 groups of four values each, one group per thread), so that all a
+// row needs is fetched at once; the CTAs' three sums meet through distributed
+// shared memory and are added in rank order by everyone.
+template <int C>
+__global__ void __launch_bounds__(1024)
+polynorm_cluster_kernel(const float *__restrict__ z, int S, size_t stride, int z_ld,
+                        const float *__restrict__ coef, float eps, bf16 *__restrict__ out, int ff,
+                        int per4)
+{
+    __shared__ float red[96];
+    __shared__ float shares[3][C];     // shares[k][r]: written here by the CTA of rank r
+    pdl_trigger();
+    float c0 = coef[0], c1 = coef[1], c2 = coef[2], c3 = coef[3];
+    uint32_t rank = cluster_rank();
+    size_t row = blockIdx.x / C;
+    int nv = ff / 4;
+    int j = (int)rank * per4 + threadIdx.x;
+    bool mine = (int)threadIdx.x < per4 && j < nv;
+    pdl_wait();
+    const float *zr = z + row * z_ld;
+    float4 v = mine ? sum_partials4(zr + 4 * j, S, stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    power_sums(v, s2, s4, s6);
+    block_sum3(s2, s4, s6, red);
+    if (threadIdx.x < C) {
+        cluster_write(&shares[0][rank], threadIdx.x, s2);
+        cluster_write(&shares[1][rank], threadIdx.x, s4);
+        cluster_write(&shares[2][rank], threadIdx.x, s6);
+    }
+    cluster_arrive();
+    cluster_wait();
+    float t2 = 0.0f, t4 = 0.0f, t6 = 0.0f;
+#pragma unroll
+    for (int r = 0; r < C; r++) {
+        t2 += shares[0][r];
+        t4 += shares[1][r];
+        t6 += shares[2][r];
+    }
+    float r1 = 1.0f / sqrtf(t2 / (float)ff + eps);
+    float r2 = 1.0f / sqrtf(t4 / (float)ff + eps);
+    float r3 = 1.0f / sqrtf(t6 / (float)ff + eps);
+    if (mine)
+        store4(out + row * ff + 4 * j, poly4(v, c0, c1, c2, c3, r1, r2, r3));
 }
 
 // z: S stacked partial sums, rows z_ld wide of which the first ff columns are the
@@ -217,6 +437,42 @@ __global__ void qkv_bias_append_kernel(const float *__restrict__ qkv, int S, siz
     }
 }
 
+// The same with four neighbouring columns per thread (hd and vd multiples of 4: the
+// four never straddle two heads).
+template <typename TC>
+__global__ void __launch_bounds__(256)
+qkv_bias_append_vec_kernel(const float *__restrict__ qkv, int S, size_t stride, int ld,
+                           const float *__restrict__ bias, const int32_t *__restrict__ row_pos,
+                           const int32_t *__restrict__ row_seq,
+                           const int32_t *__restrict__ block_table, int bt_stride,
+                           TC *__restrict__ q_out, TC *__restrict__ k_cache,
+                           TC *__restrict__ v_cache, int nh, int nkv, int hd, int vd, int width)
+{
+    pdl_trigger();
+    size_t row = blockIdx.x;
+    int c = (int)(blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= width)
+        return;
+    float4 bv = bias ? load4(bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    int qw = nh * hd, kw = nkv * hd;
+    int pos = 0, page = 0;
+    if (c >= qw) {
+        pos = row_pos[row];
+        page = block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE];
+    }
+    pdl_wait();
+    float4 v = add4(sum_partials4(qkv + row * ld + c, S, stride), bv);
+    if (c < qw) {
+        store4(q_out + row * qw + c, v);
+    } else if (c < qw + kw) {
+        int kc = c - qw, h = kc / hd, d = kc - h * hd;
+        store4(k_cache + (((size_t)page * nkv + h) * PAGE + pos % PAGE) * hd + d, v);
+    } else {
+        int vc = c - qw - kw, h = vc / vd, d = vc - h * vd;
+        store4(v_cache + (((size_t)page * nkv + h) * PAGE + pos % PAGE) * vd + d, v);
+    }
+}
+
 static int row_threads(int width)
 {
     int t = 32;
@@ -291,11 +547,38 @@ extern "C" int jb_gated_dyt_residual(float *x, const float *y, int Sy, long long
                                      long long g_stride, int g_ld, int g_col0, const float *g_bias,
                                      const float *pw, const float *pb, const float *palpha,
                                      const float *nw, const float *nb, const float *nalpha,
-                                     void *out, int out_dt, int n, int dm, cudaStream_t st)
+                                     void *out, int out_dt, int n, int dm, int fast,
+                                     cudaStream_t st)
 {
     size_t total = (size_t)n * dm;
     if (total == 0)
         return JB_OK;
+    auto al16 = [](const void *p) { return (uintptr_t)p % 16 == 0; };
+    if (dm % 4 == 0 && g_ld % 4 == 0 && g_col0 % 4 == 0 && y_stride % 4 == 0 && g_stride % 4 == 0 &&
+        al16(x) && al16(y) && al16(g) && al16(y_bias) && al16(g_bias) && al16(pw) && al16(pb) &&
+        al16(nw) && al16(nb) && (uintptr_t)out % 8 == 0 && (out == nullptr || out_dt == JB_F32 ||
+                                                             out_dt == JB_BF16)) {
+        unsigned threads = (unsigned)min(256, (dm / 4 + 31) / 32 * 32);
+        dim3 grid((unsigned)n, (unsigned)((dm / 4 + threads - 1) / threads));
+        // the bfloat16 path (fast says so: the last layer's call has no norm output
+        // to tell it by) takes the hardware's exponential
+        if (fast && (out == nullptr || out_dt == JB_BF16)) {
+            launch(gated_dyt_residual_vec_kernel<bf16, true>, grid, threads, 0, st, x, y, Sy,
+                   (size_t)y_stride, y_bias, g, Sg, (size_t)g_stride, g_ld, g_col0, g_bias, pw, pb,
+                   palpha, nw, nb, nalpha, (bf16 *)out, dm);
+        } else if (out == nullptr || out_dt == JB_F32) {
+            if (!al16(out))
+                return JB_EINVAL;
+            launch(gated_dyt_residual_vec_kernel<float, false>, grid, threads, 0, st, x, y, Sy,
+                   (size_t)y_stride, y_bias, g, Sg, (size_t)g_stride, g_ld, g_col0, g_bias, pw, pb,
+                   palpha, nw, nb, nalpha, (float *)out, dm);
+        } else {
+            launch(gated_dyt_residual_vec_kernel<bf16, false>, grid, threads, 0, st, x, y, Sy,
+                   (size_t)y_stride, y_bias, g, Sg, (size_t)g_stride, g_ld, g_col0, g_bias, pw, pb,
+                   palpha, nw, nb, nalpha, (bf16 *)out, dm);
+        }
+        return launch_status();
+    }
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (out == nullptr || out_dt == JB_F32)
         launch(gated_dyt_residual_kernel<float>, blocks, 256, 0, st, x, y, Sy, (size_t)y_stride,
@@ -315,6 +598,52 @@ extern "C" int jb_polynorm(const float *z, int S, long long stride, int z_ld, co
 {
     if (n <= 0 || ff <= 0)
         return JB_OK;
+    bool vec = ff % 4 == 0 && z_ld % 4 == 0 && stride % 4 == 0 && (uintptr_t)z % 16 == 0 &&
+               (uintptr_t)out % (out_dt == JB_F32 ? 16 : 8) == 0;
+    // few rows of the bfloat16 path: a cluster of eight CTAs per row
+    if (vec && out_dt == JB_BF16 && n <= 32 && ff >= 2048 && ff <= 8 * 4 * 1024) {
+        constexpr int C = 8;
+        int per4 = (ff / 4 + C - 1) / C;
+        unsigned threads = (unsigned)((per4 + 31) / 32 * 32);
+        launch_cluster(polynorm_cluster_kernel<C>, dim3((unsigned)n * C), threads, 0, st, C, z, S,
+                       (size_t)stride, z_ld, coef, eps, (bf16 *)out, ff, per4);
+        return launch_status();
+    }
+    if (vec && ff <= 8 * 4 * 512 && (out_dt == JB_F32 || out_dt == JB_BF16)) {
+        int nv = ff / 4;
+        // threads and values per thread depend on ff alone
+        int keep = nv <= 512 ? 1 : (nv + 511) / 512;
+        unsigned threads = (unsigned)(((nv + keep - 1) / keep + 31) / 32 * 32);
+#define JB_PN(TO, K)                                                                          \
+    launch(polynorm_vec_kernel<TO, K>, n, threads, 0, st, z, S, (size_t)stride, z_ld, coef, eps, \
+           (TO *)out, ff)
+#define JB_PNK(TO)                                                                            \
+    do {                                                                                       \
+        if (keep == 1)                                                                         \
+            JB_PN(TO, 1);                                                                      \
+        else if (keep == 2)                                                                    \
+            JB_PN(TO, 2);                                                                      \
+        else if (keep == 3)                                                                    \
+            JB_PN(TO, 3);                                                                      \
+        else if (keep == 4)                                                                    \
+            JB_PN(TO, 4);                                                                      \
+        else if (keep == 5)                                                                    \
+            JB_PN(TO, 5);                                                                      \
+        else if (keep == 6)                                                                    \
+            JB_PN(TO, 6);                                                                      \
+        else if (keep == 7)                                                                    \
+            JB_PN(TO, 7);                                                                      \
+        else                                                                                   \
+            JB_PN(TO, 8);                                                                      \
+    } while (0)
+        if (out_dt == JB_F32)
+            JB_PNK(float);
+        else
+            JB_PNK(bf16);
+#undef JB_PN
+#undef JB_PNK
+        return launch_status();
+    }
     int threads = row_threads(ff);
     if (out_dt == JB_F32)
         launch(polynorm_kernel<float>, n, threads, 0, st, z, S, (size_t)stride, z_ld, coef, eps,
@@ -359,6 +688,23 @@ extern "C" int jb_qkv_bias_append(const float *qkv, int S, long long stride, int
     if (ld < width)
         return JB_EINVAL;
     size_t total = (size_t)n * width;
+    size_t esz = cache_dt == JB_F32 ? 4 : 2;
+    if (hd % 4 == 0 && (!append || vd % 4 == 0) && ld % 4 == 0 && stride % 4 == 0 &&
+        (uintptr_t)qkv % 16 == 0 && (uintptr_t)bias % 16 == 0 && (uintptr_t)q_out % (4 * esz) == 0 &&
+        (uintptr_t)k_cache % (4 * esz) == 0 && (uintptr_t)v_cache % (4 * esz) == 0 &&
+        (cache_dt == JB_F32 || cache_dt == JB_BF16)) {
+        unsigned threads = (unsigned)min(256, (width / 4 + 31) / 32 * 32);
+        dim3 grid((unsigned)n, (unsigned)((width / 4 + threads - 1) / threads));
+        if (cache_dt == JB_F32)
+            launch(qkv_bias_append_vec_kernel<float>, grid, threads, 0, st, qkv, S, (size_t)stride, ld,
+                   bias, row_pos, row_seq, block_table, bt_stride, (float *)q_out, (float *)k_cache,
+                   (float *)v_cache, nh, nkv, hd, vd, width);
+        else
+            launch(qkv_bias_append_vec_kernel<bf16>, grid, threads, 0, st, qkv, S, (size_t)stride, ld,
+                   bias, row_pos, row_seq, block_table, bt_stride, (bf16 *)q_out, (bf16 *)k_cache,
+                   (bf16 *)v_cache, nh, nkv, hd, vd, width);
+        return launch_status();
+    }
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (cache_dt == JB_F32)
         launch(qkv_bias_append_kernel<float>, blocks, 256, 0, st, qkv, S, (size_t)stride, ld, bias,

@@ -70,7 +70,7 @@ int jb_gated_dyt_residual(float *x, const float *y, int Sy, long long y_stride,
                           const float *y_bias, const float *g, int Sg, long long g_stride,
                           int g_ld, int g_col0, const float *g_bias, const float *pw,
                           const float *pb, const float *palpha, const float *nw, const float *nb,
-                          const float *nalpha, void *out, int out_dt, int n, int dm,
+                          const float *nalpha, void *out, int out_dt, int n, int dm, int fast,
                           cudaStream_t st);
 int jb_polynorm(const float *z, int S, long long stride, int z_ld, const float *coef, float eps,
                 void *out, int out_dt, int n, int ff, cudaStream_t st);

@@ -103,7 +103,7 @@ Buf gated_dyt_residual(Device &d, float *x, const Stack &y, const Stack &g, long
                                 as_int(g.m, "width"), (int)g_col0, g_bias, post.w, post.b, post.alpha,
                                 next ? next->w : nullptr, next ? next->b : nullptr,
                                 next ? next->alpha : nullptr, out.ptr, out_dt, as_int(y.n, "rows"),
-                                as_int(y.m, "width"), d.stream), "gated_dyt_residual");
+                                as_int(y.m, "width"), out_dt == BF16 ? 1 : 0, d.stream), "gated_dyt_residual");
     return out;
 }
 
@@ -344,8 +344,7 @@ Buf attention_decode_qkv(Device &d, const Stack &qkv, const DevTensor *q_w, cons
     if (c.dt != BF16 || !c.k || !jb_attn_tc_decode_runs(g.nh, g.nkv, g.hd) || g.value_dim() != g.hd)
         return Buf();
     long long width = (long long)(g.nh + (c.writes ? 2 * g.nkv : 0)) * g.hd;
-    if (qkv.m != width && qkv.m != (long long)(g.nh + 2 * g.nkv) * g.hd)
-        fail(JB_LLM_EINVAL, "attention: qkv is not heads + 2 kv_heads wide");
+    if (qkv.m < width) fail(JB_LLM_EINVAL, "attention: qkv is narrower than the heads it holds");
     int w_dt = 0;
     if (q_w) {
         if (!k_w || q_w->dt != k_w->dt) fail(JB_LLM_EINVAL, "attention: q and k norm weights of one type");

@@ -348,7 +348,8 @@ def gated_dyt_residual(x: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.
     _check(lib().jb_gated_dyt_residual(_p(x), _p(y), y.shape[0], n * dm, _p(y_bias), _p(g),
                                        g.shape[0], n * g.shape[2], g.shape[2], 0, _p(g_bias),
                                        _p(post[0]), _p(post[1]), _p(post[2]), _p(nw), _p(nb),
-                                       _p(na), _p(out), _DT[out_dtype], n, dm, _stream()),
+                                       _p(na), _p(out), _DT[out_dtype], n, dm,
+                                       1 if out_dtype == torch.bfloat16 else 0, _stream()),
            "gated_dyt_residual")
     return out
 

@@ -269,6 +269,17 @@ public:
         return own_kv_ ? KVSpec{g_.nkv, g_.hd, g_.window, g_.vd} : KVSpec();
     }
 
+    bool take_side_rows(DevTensor &m) override {
+        if (!w_in_ || m.shape.size() != 2 || m.shape[1] != hidden_ || side_cols_ > 0) return false;
+        side_col0_ = w_in_.shape[0];
+        side_cols_ = m.shape[0];
+        std::vector<DevTensor> both = {w_in_, m};
+        w_in_ = DevTensor();
+        m = DevTensor();
+        w_in_ = fuse_rows(*dev, both);
+        return true;
+    }
+
     void prepare(long long) override { chunk_ = ops::attention_chunk(); }
     bool supports(StepKind) const override { return true; }
     bool graph_safe() const override { return true; }
@@ -295,10 +306,13 @@ public:
             // value from the product's sums and its bias itself, where it takes the sizes
             Buf a = ops::attention_decode_qkv(d, qkv, nullptr, nullptr, 0.0f, nullptr, nullptr, cache.kv, g_,
                                               ctx.row_pos, ctx.row_seq, max_chunks, b_in);
-            if (a) return output(ctx, a);
+            if (a) {
+                keep_side(ctx, qkv);
+                return output(ctx, a);
+            }
         }
         Buf q = ops::qkv_bias_append(d, qkv, b_in, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype, own_kv_);
-        qkv.buf.reset();
+        keep_side(ctx, qkv);
         const int32_t *blocks = nullptr;
         int n_blocks = 0;
         if (!decode && ctx.dtype == BF16 && ops::attention_tc_ok(g_.nh, g_.nkv, g_.hd) && g_.vd == g_.hd &&
@@ -318,6 +332,15 @@ public:
         Buf a = ops::attention(d, q.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, blocks, n_blocks,
                                decode);
         return output(ctx, a);
+    }
+
+    // the product goes to whoever gave the side rows, or back to the pool
+    void keep_side(StepContext &ctx, Stack &qkv) {
+        if (side_cols_ > 0) {
+            ctx.side = std::move(qkv);
+            ctx.side_col0 = side_col0_;
+        }
+        qkv = Stack();
     }
 
     Stack output(StepContext &ctx, const Buf &a) {
@@ -342,6 +365,7 @@ private:
     bool bias_, head_scale_, sink_, own_kv_;
     std::string n_q_, n_k_, n_v_, n_o_, n_bias_, n_hs_, n_sink_;
     DevTensor w_in_, b_in_, w_o_, b_o_, temp_, sinks_;
+    long long side_col0_ = 0, side_cols_ = 0;
     int chunk_ = 0;
 };
 

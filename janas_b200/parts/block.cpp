@@ -72,11 +72,17 @@ public:
             if (gate_name_[i].empty()) continue;
             gate_[i] = Part::take(t, Part::name(prefix, gate_name_[i]));
             if (!bias_suffix_.empty()) gate_bias_[i] = Part::take(t, Part::name(prefix, gate_name_[i] + bias_suffix_));
+            // the gate reads what its sublayer reads: one product for both, where the part can
+            if (fuse_) {
+                Part *p = i == 0 ? (Part *)mixer.get() : (Part *)feed_forward.get();
+                in_part_[i] = p->take_side_rows(gate_[i]);
+            }
         }
         for (auto &u : unused_) t.erase(Part::name(prefix, u.first));
     }
 
     size_t weight_bytes() const override {
+        // a gate that went into its sublayer's first product is counted there
         return gate_[0].bytes() + gate_[1].bytes() + gate_bias_[0].bytes() + gate_bias_[1].bytes();
     }
 
@@ -89,8 +95,9 @@ public:
         {
             Stack g = gate_product(ctx, 0, h.ptr);
             Stack y = mixer->forward(ctx, h.ptr, cache);
+            long long col0 = take_side(ctx, 0, g);
             const Norm *next = feed_forward ? ffn_norm.get() : next_norm;
-            finish(ctx, x, y, g, 0, post_mixer_norm.get(), next);
+            finish(ctx, x, y, g, col0, 0, post_mixer_norm.get(), next);
         }
         if (!feed_forward) return;
         h = take_normed(ctx, ffn_norm.get());
@@ -98,7 +105,8 @@ public:
         {
             Stack g = gate_product(ctx, 1, h.ptr);
             Stack y = feed_forward->forward(ctx, h.ptr);
-            finish(ctx, x, y, g, 1, post_ffn_norm.get(), next_norm);
+            long long col0 = take_side(ctx, 1, g);
+            finish(ctx, x, y, g, col0, 1, post_ffn_norm.get(), next_norm);
         }
     }
 
@@ -113,6 +121,15 @@ private:
         return std::move(ctx.normed);
     }
 
+    // the gate's values out of the sublayer's own first product, where they went into it
+    long long take_side(StepContext &ctx, int which, Stack &g) {
+        if (!in_part_[which]) return 0;
+        if (!ctx.side) fail(JB_LLM_EFAIL, "sandwich: the sublayer took the gate's rows and left no product");
+        g = std::move(ctx.side);
+        ctx.side = Stack();
+        return ctx.side_col0;
+    }
+
     Stack gate_product(StepContext &ctx, int which, const void *h) {
         if (!gate_[which]) return Stack();
         return ops::linear(*ctx.dev, h, ctx.dtype, ctx.n_rows, hidden_, gate_[which]);
@@ -120,14 +137,15 @@ private:
 
     // x += norm_out(y * gate); the next norm of x too where both norms work value by
     // value (its result then waits in ctx.normed)
-    void finish(StepContext &ctx, float *x, Stack &y, const Stack &g, int which, Norm *post, const Norm *next) {
+    void finish(StepContext &ctx, float *x, Stack &y, const Stack &g, long long col0, int which, Norm *post,
+                const Norm *next) {
         Device &d = *ctx.dev;
         long long n = ctx.n_rows;
         const float *g_bias = gate_bias_[which] ? (const float *)gate_bias_[which].ptr : nullptr;
         ops::DytParams pp, np;
         if (fuse_ && g && post->dynamic_tanh(&pp)) {
             bool fuse_next = next && next->dynamic_tanh(&np);
-            Buf out = ops::gated_dyt_residual(d, x, y, g, 0, g_bias, pp, fuse_next ? &np : nullptr, ctx.dtype);
+            Buf out = ops::gated_dyt_residual(d, x, y, g, col0, g_bias, pp, fuse_next ? &np : nullptr, ctx.dtype);
             if (fuse_next) {
                 ctx.normed = std::move(out);
                 ctx.normed_by = next;
@@ -138,7 +156,7 @@ private:
         Buf t;
         Stack one;
         if (g) {
-            t = ops::gate_mul(d, y, g, 0, g_bias);
+            t = ops::gate_mul(d, y, g, col0, g_bias);
         } else {
             t = d.pool.get((size_t)n * (size_t)hidden_ * 4);
             cuda_check(cudaMemsetAsync(t.ptr, 0, t.bytes, d.stream), "clearing a sum");
@@ -156,6 +174,7 @@ private:
     bool fuse_ = true;      // false: every step as a kernel of its own (for comparisons)
     std::string gate_name_[2], bias_suffix_;
     DevTensor gate_[2], gate_bias_[2];
+    bool in_part_[2] = {false, false};     // the gate's rows lie in the sublayer's first product
     std::vector<std::pair<std::string, std::vector<long long>>> unused_;
 };
 

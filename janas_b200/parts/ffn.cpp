@@ -111,12 +111,26 @@ public:
 
     size_t weight_bytes() const override { return w_up_.bytes() + w_down_.bytes() + coef_.bytes(); }
 
+    bool take_side_rows(DevTensor &m) override {
+        if (!w_up_ || m.shape.size() != 2 || m.shape[1] != hidden_ || side_) return false;
+        std::vector<DevTensor> both = {w_up_, m};
+        w_up_ = DevTensor();
+        m = DevTensor();
+        w_up_ = fuse_rows(*dev, both);
+        side_ = true;
+        return true;
+    }
+
     Stack forward(StepContext &ctx, const void *h) override {
         Device &d = *ctx.dev;
         long long n = ctx.n_rows;
         Stack z = ops::linear(d, h, ctx.dtype, n, hidden_, w_up_);
         Buf act = ops::polynorm(d, z, inter_, (const float *)coef_.ptr, eps_, ctx.dtype);
-        z.buf.reset();
+        if (side_) {
+            ctx.side = std::move(z);
+            ctx.side_col0 = inter_;
+        }
+        z = Stack();
         return ops::linear(d, act.ptr, ctx.dtype, n, inter_, w_down_);
     }
 
@@ -125,6 +139,7 @@ private:
     float eps_;
     std::string n_up_, n_down_, n_coef_;
     DevTensor w_up_, w_down_, coef_;
+    bool side_ = false;     // the up matrix carries side rows after its own
 };
 
 }  // namespace

@@ -82,6 +82,10 @@ struct StepContext {
     // that norm next.
     Buf normed;
     const Norm *normed_by = nullptr;
+    // The whole first product of the part that ran last, when it took side rows into
+    // it (Part::take_side_rows): their columns start at side_col0.
+    Stack side;
+    long long side_col0 = 0;
 };
 
 using TensorMap = std::map<std::string, DevTensor>;
@@ -97,6 +101,12 @@ public:
     virtual void load(const std::string &prefix, TensorMap &t) {}
     virtual size_t weight_bytes() const { return 0; }
     virtual Json info() const { return Json::object(); }
+    // Side rows: a matrix over the part's own input that belongs to someone else (a
+    // block's gate).  A part that can takes it into its first product, so that one
+    // kernel serves both; its forward() then leaves that whole product in ctx.side
+    // and says in ctx.side_col0 where the side rows' columns start.  False (and
+    // nothing taken) where the part cannot.  Called after load().
+    virtual bool take_side_rows(DevTensor &m) { return false; }
 
     PartSpec spec;
     DType dtype;
