@@ -174,22 +174,25 @@ __global__ void gated_dyt_residual_kernel(
 
 // The same with four neighbouring columns per thread (dm, the gate's row length and
 // first column multiples of 4, everything at 16-byte boundaries).
-// Grid: x over rows, y over blocks of columns (no division per thread).
-template <typename TO, bool FAST>
+// Grid: x over groups of GDR_ROWS rows, y over blocks of columns (no division per
+// thread); with two rows a thread fetches its columns' parameters once for both and
+// has both rows' values in flight together (many rows); with one, more threads share
+// the work (few rows, many partial sums).
+template <typename TO, bool FAST, int GDR_ROWS>
 __global__ void __launch_bounds__(256)
 gated_dyt_residual_vec_kernel(
     float *__restrict__ x, const float *__restrict__ y, int Sy, size_t y_stride,
     const float *__restrict__ y_bias, const float *__restrict__ g, int Sg, size_t g_stride,
     int g_ld, int g_col0, const float *__restrict__ g_bias, const float *__restrict__ pw,
     const float *__restrict__ pb, const float *__restrict__ palpha, const float *__restrict__ nw,
-    const float *__restrict__ nb, const float *__restrict__ nalpha, TO *__restrict__ out, int dm)
+    const float *__restrict__ nb, const float *__restrict__ nalpha, TO *__restrict__ out, int dm,
+    int n)
 {
     pdl_trigger();
-    size_t row = blockIdx.x;
+    size_t row0 = (size_t)blockIdx.x * GDR_ROWS;
     int c = (int)(blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (c >= dm)
         return;
-    size_t i = row * dm + c;
     float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     float4 yb = y_bias ? load4(y_bias + c) : zero, gb = g_bias ? load4(g_bias + c) : zero;
     float4 pwv = load4(pw + c), pbv = load4(pb + c);
@@ -202,17 +205,34 @@ gated_dyt_residual_vec_kernel(
         na = nalpha[0];
     }
     pdl_wait();
-    float4 xv = load4(x + i);
-    float4 yv = add4(sum_partials4(y + i, Sy, y_stride), yb);
-    float4 gv = add4(sum_partials4(g + row * g_ld + g_col0 + c, Sg, g_stride), gb);
-    xv.x += dyt_f<FAST>(yv.x * sigmoid_f<FAST>(gv.x), pa, pwv.x, pbv.x);
-    xv.y += dyt_f<FAST>(yv.y * sigmoid_f<FAST>(gv.y), pa, pwv.y, pbv.y);
-    xv.z += dyt_f<FAST>(yv.z * sigmoid_f<FAST>(gv.z), pa, pwv.z, pbv.z);
-    xv.w += dyt_f<FAST>(yv.w * sigmoid_f<FAST>(gv.w), pa, pwv.w, pbv.w);
-    store4(x + i, xv);
-    if (out != nullptr)
-        store4(out + i, make_float4(dyt_f<FAST>(xv.x, na, nwv.x, nbv.x), dyt_f<FAST>(xv.y, na, nwv.y, nbv.y),
-                                    dyt_f<FAST>(xv.z, na, nwv.z, nbv.z), dyt_f<FAST>(xv.w, na, nwv.w, nbv.w)));
+    float4 xs[GDR_ROWS], ys[GDR_ROWS], gs[GDR_ROWS];
+#pragma unroll
+    for (int r = 0; r < GDR_ROWS; r++) {
+        size_t row = row0 + r;
+        if (row < (size_t)n) {
+            size_t i = row * dm + c;
+            xs[r] = load4(x + i);
+            ys[r] = sum_partials4(y + i, Sy, y_stride);
+            gs[r] = sum_partials4(g + row * g_ld + g_col0 + c, Sg, g_stride);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < GDR_ROWS; r++) {
+        size_t row = row0 + r;
+        if (row >= (size_t)n)
+            break;
+        size_t i = row * dm + c;
+        float4 xv = xs[r], yv = add4(ys[r], yb), gv = add4(gs[r], gb);
+        xv.x += dyt_f<FAST>(yv.x * sigmoid_f<FAST>(gv.x), pa, pwv.x, pbv.x);
+        xv.y += dyt_f<FAST>(yv.y * sigmoid_f<FAST>(gv.y), pa, pwv.y, pbv.y);
+        xv.z += dyt_f<FAST>(yv.z * sigmoid_f<FAST>(gv.z), pa, pwv.z, pbv.z);
+        xv.w += dyt_f<FAST>(yv.w * sigmoid_f<FAST>(gv.w), pa, pwv.w, pbv.w);
+        store4(x + i, xv);
+        if (out != nullptr)
+            store4(out + i,
+                   make_float4(dyt_f<FAST>(xv.x, na, nwv.x, nbv.x), dyt_f<FAST>(xv.y, na, nwv.y, nbv.y),
+                               dyt_f<FAST>(xv.z, na, nwv.z, nbv.z), dyt_f<FAST>(xv.w, na, nwv.w, nbv.w)));
+    }
 }
 
 __device__ __forceinline__ void power_sums(float4 v, float &s2, float &s4, float &s6)
@@ -438,38 +458,62 @@ __global__ void qkv_bias_append_kernel(const float *__restrict__ qkv, int S, siz
 }
 
 // The same with four neighbouring columns per thread (hd and vd multiples of 4: the
-// four never straddle two heads).
-template <typename TC>
+// four never straddle two heads), for ROWS rows each (grid: x over groups of rows, y
+// over blocks of columns).
+template <typename TC, int ROWS>
 __global__ void __launch_bounds__(256)
 qkv_bias_append_vec_kernel(const float *__restrict__ qkv, int S, size_t stride, int ld,
                            const float *__restrict__ bias, const int32_t *__restrict__ row_pos,
                            const int32_t *__restrict__ row_seq,
                            const int32_t *__restrict__ block_table, int bt_stride,
                            TC *__restrict__ q_out, TC *__restrict__ k_cache,
-                           TC *__restrict__ v_cache, int nh, int nkv, int hd, int vd, int width)
+                           TC *__restrict__ v_cache, int nh, int nkv, int hd, int vd, int width,
+                           int n)
 {
     pdl_trigger();
-    size_t row = blockIdx.x;
+    size_t row0 = (size_t)blockIdx.x * ROWS;
     int c = (int)(blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (c >= width)
         return;
     float4 bv = bias ? load4(bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     int qw = nh * hd, kw = nkv * hd;
-    int pos = 0, page = 0;
-    if (c >= qw) {
-        pos = row_pos[row];
-        page = block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE];
+    // where this thread's four values go within a row of q, or within a head of the cache
+    bool is_q = c < qw, is_k = !is_q && c < qw + kw;
+    int h = 0, d = 0;
+    if (is_k) {
+        h = (c - qw) / hd;
+        d = (c - qw) - h * hd;
+    } else if (!is_q) {
+        h = (c - qw - kw) / vd;
+        d = (c - qw - kw) - h * vd;
+    }
+    int pos[ROWS], page[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; r++) {
+        pos[r] = page[r] = 0;
+        if (!is_q && row0 + r < (size_t)n) {
+            pos[r] = row_pos[row0 + r];
+            page[r] = block_table[(size_t)row_seq[row0 + r] * bt_stride + pos[r] / PAGE];
+        }
     }
     pdl_wait();
-    float4 v = add4(sum_partials4(qkv + row * ld + c, S, stride), bv);
-    if (c < qw) {
-        store4(q_out + row * qw + c, v);
-    } else if (c < qw + kw) {
-        int kc = c - qw, h = kc / hd, d = kc - h * hd;
-        store4(k_cache + (((size_t)page * nkv + h) * PAGE + pos % PAGE) * hd + d, v);
-    } else {
-        int vc = c - qw - kw, h = vc / vd, d = vc - h * vd;
-        store4(v_cache + (((size_t)page * nkv + h) * PAGE + pos % PAGE) * vd + d, v);
+    float4 v[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; r++)
+        if (row0 + r < (size_t)n)
+            v[r] = sum_partials4(qkv + (row0 + r) * ld + c, S, stride);
+#pragma unroll
+    for (int r = 0; r < ROWS; r++) {
+        size_t row = row0 + r;
+        if (row >= (size_t)n)
+            break;
+        float4 o = add4(v[r], bv);
+        if (is_q)
+            store4(q_out + row * qw + c, o);
+        else if (is_k)
+            store4(k_cache + (((size_t)page[r] * nkv + h) * PAGE + pos[r] % PAGE) * hd + d, o);
+        else
+            store4(v_cache + (((size_t)page[r] * nkv + h) * PAGE + pos[r] % PAGE) * vd + d, o);
     }
 }
 
@@ -558,25 +602,36 @@ extern "C" int jb_gated_dyt_residual(float *x, const float *y, int Sy, long long
         al16(x) && al16(y) && al16(g) && al16(y_bias) && al16(g_bias) && al16(pw) && al16(pb) &&
         al16(nw) && al16(nb) && (uintptr_t)out % 8 == 0 && (out == nullptr || out_dt == JB_F32 ||
                                                              out_dt == JB_BF16)) {
+        // blocks that the row's groups of four fill without idle threads, where that can be
         unsigned threads = (unsigned)min(256, (dm / 4 + 31) / 32 * 32);
-        dim3 grid((unsigned)n, (unsigned)((dm / 4 + threads - 1) / threads));
+        if (dm / 4 > 256 && (dm / 4) % 128 == 0 && (dm / 4) % 256 != 0)
+            threads = 128;
         // the bfloat16 path (fast says so: the last layer's call has no norm output
         // to tell it by) takes the hardware's exponential
+        int rows_per = n >= 64 ? 2 : 1;
+        dim3 grid((unsigned)((n + rows_per - 1) / rows_per), (unsigned)((dm / 4 + threads - 1) / threads));
+#define JB_GDR(TO, F, R)                                                                      \
+    launch(gated_dyt_residual_vec_kernel<TO, F, R>, grid, threads, 0, st, x, y, Sy,            \
+           (size_t)y_stride, y_bias, g, Sg, (size_t)g_stride, g_ld, g_col0, g_bias, pw, pb,    \
+           palpha, nw, nb, nalpha, (TO *)out, dm, n)
+#define JB_GDR_R(TO, F)                                                                       \
+    do {                                                                                       \
+        if (rows_per == 2)                                                                     \
+            JB_GDR(TO, F, 2);                                                                  \
+        else                                                                                   \
+            JB_GDR(TO, F, 1);                                                                  \
+    } while (0)
         if (fast && (out == nullptr || out_dt == JB_BF16)) {
-            launch(gated_dyt_residual_vec_kernel<bf16, true>, grid, threads, 0, st, x, y, Sy,
-                   (size_t)y_stride, y_bias, g, Sg, (size_t)g_stride, g_ld, g_col0, g_bias, pw, pb,
-                   palpha, nw, nb, nalpha, (bf16 *)out, dm);
+            JB_GDR_R(bf16, true);
         } else if (out == nullptr || out_dt == JB_F32) {
             if (!al16(out))
                 return JB_EINVAL;
-            launch(gated_dyt_residual_vec_kernel<float, false>, grid, threads, 0, st, x, y, Sy,
-                   (size_t)y_stride, y_bias, g, Sg, (size_t)g_stride, g_ld, g_col0, g_bias, pw, pb,
-                   palpha, nw, nb, nalpha, (float *)out, dm);
+            JB_GDR_R(float, false);
         } else {
-            launch(gated_dyt_residual_vec_kernel<bf16, false>, grid, threads, 0, st, x, y, Sy,
-                   (size_t)y_stride, y_bias, g, Sg, (size_t)g_stride, g_ld, g_col0, g_bias, pw, pb,
-                   palpha, nw, nb, nalpha, (bf16 *)out, dm);
+            JB_GDR_R(bf16, false);
         }
+#undef JB_GDR
+#undef JB_GDR_R
         return launch_status();
     }
     unsigned blocks = (unsigned)((total + 255) / 256);
@@ -694,15 +749,21 @@ extern "C" int jb_qkv_bias_append(const float *qkv, int S, long long stride, int
         (uintptr_t)k_cache % (4 * esz) == 0 && (uintptr_t)v_cache % (4 * esz) == 0 &&
         (cache_dt == JB_F32 || cache_dt == JB_BF16)) {
         unsigned threads = (unsigned)min(256, (width / 4 + 31) / 32 * 32);
-        dim3 grid((unsigned)n, (unsigned)((width / 4 + threads - 1) / threads));
-        if (cache_dt == JB_F32)
-            launch(qkv_bias_append_vec_kernel<float>, grid, threads, 0, st, qkv, S, (size_t)stride, ld,
-                   bias, row_pos, row_seq, block_table, bt_stride, (float *)q_out, (float *)k_cache,
-                   (float *)v_cache, nh, nkv, hd, vd, width);
+        int rows_per = n >= 64 ? 2 : 1;
+        dim3 grid((unsigned)((n + rows_per - 1) / rows_per), (unsigned)((width / 4 + threads - 1) / threads));
+#define JB_APP(TC, R)                                                                         \
+    launch(qkv_bias_append_vec_kernel<TC, R>, grid, threads, 0, st, qkv, S, (size_t)stride, ld, \
+           bias, row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache,         \
+           (TC *)v_cache, nh, nkv, hd, vd, width, n)
+        if (cache_dt == JB_F32 && rows_per == 2)
+            JB_APP(float, 2);
+        else if (cache_dt == JB_F32)
+            JB_APP(float, 1);
+        else if (rows_per == 2)
+            JB_APP(bf16, 2);
         else
-            launch(qkv_bias_append_vec_kernel<bf16>, grid, threads, 0, st, qkv, S, (size_t)stride, ld,
-                   bias, row_pos, row_seq, block_table, bt_stride, (bf16 *)q_out, (bf16 *)k_cache,
-                   (bf16 *)v_cache, nh, nkv, hd, vd, width);
+            JB_APP(bf16, 1);
+#undef JB_APP
         return launch_status();
     }
     unsigned blocks = (unsigned)((total + 255) / 256);

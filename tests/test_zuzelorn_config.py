@@ -50,3 +50,17 @@ def test_refusals():
     bad(lambda c: c["layers"][0]["mixer"].update(heads=3))
     bad(lambda c: c.pop("width"))
     bad(lambda c: c["norm"].pop("eps"))
+
+
+def test_random_model_folder(tmp_path):
+    """The folder writer makes a model of the design that the loader accepts as a whole."""
+    import torch
+    from janas_b200.config import config_from_dir
+    from janas_b200.weights import check_folder, list_folder, write_random_model
+    c = config_from_dict(CONFIGS["ZD"])
+    write_random_model(str(tmp_path), c, seed=3, dtype=torch.bfloat16)
+    back = config_from_dir(str(tmp_path))
+    assert back.to_dict() == c.to_dict()
+    check_folder(str(tmp_path), expected_tensors(back.to_model_spec()))
+    have = list_folder(str(tmp_path))
+    assert have["l0.norm1.alpha"][1] == () and have["l2.mix.q"][1] == (6 * 24, 50) and "l2.mix.k" not in have

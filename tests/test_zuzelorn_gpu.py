@@ -98,6 +98,36 @@ def test_embed_with_positions():
         assert torch.equal(got[0], want[0])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,vd,extra", [(4, 2, 16, 32, 0), (3, 3, 10, 6, 0), (2, 1, 64, 64, 128)])
+def test_biased_append(dtype, nh, nkv, hd, vd, extra):
+    """q out, K and V into shuffled pages at the rows' positions, from partial sums and a bias;
+    `extra` more columns follow q, k and v in the product (another matrix's rows)."""
+    lens, rows = [70, 130], [(60, 10), (0, 130)]
+    n = sum(c for _, c in rows)
+    width = nh * hd + nkv * (hd + vd)
+    prod = rnd(2, n, width + extra, seed=5)
+    bias = rnd(width, seed=6)
+    P = Paged(lens, nkv, hd, vd, dtype, 9)
+    kc, vc = (torch.zeros(P.n_pages, nkv, PAGE, d, dtype=dtype, device=DEV) for d in (hd, vd))
+    row_pos = torch.tensor([p for (p0, cnt) in rows for p in range(p0, p0 + cnt)], dtype=torch.int32)
+    row_seq = torch.tensor([i for i, (p0, cnt) in enumerate(rows) for _ in range(cnt)], dtype=torch.int32)
+    q = ops().qkv_bias_append(prod.to(DEV), bias.to(DEV), row_pos.to(DEV), row_seq.to(DEV), P.table.to(DEV),
+                              kc, vc, nh, hd, dtype).float().cpu()
+    full = (prod.sum(0)[:, :width] + bias)
+    want = full.to(dtype).float()
+    assert torch.equal(q.reshape(n, -1), want[:, :nh * hd])
+    kc, vc = kc.float().cpu(), vc.float().cpu()
+    for r in range(n):
+        pg, at = int(P.table[row_seq[r], row_pos[r] // PAGE]), int(row_pos[r]) % PAGE
+        assert torch.equal(kc[pg, :, at].reshape(-1), want[r, nh * hd:nh * hd + nkv * hd])
+        assert torch.equal(vc[pg, :, at].reshape(-1), want[r, nh * hd + nkv * hd:])
+    # a product that holds q alone
+    q = ops().qkv_bias_append(prod[:, :, :nh * hd].contiguous().to(DEV), bias[:nh * hd].contiguous().to(DEV),
+                              row_pos.to(DEV), row_seq.to(DEV), P.table.to(DEV), None, None, nh, hd, dtype)
+    assert torch.equal(q.float().cpu().reshape(n, -1), want[:, :nh * hd])
+
+
 # ------------------------------------------------------------------ attention
 class Paged:
     """Keys and values of several sequences in pages that lie in no order."""

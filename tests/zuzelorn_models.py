@@ -31,9 +31,11 @@ def config(width, vocab, max_positions, layers, eps=1e-5, logit_scale=1.0):
 ZA = config(64, 130, 400, [attn(4, 2, 16, 32, 0.3, ff=96), attn(4, 2, 16, 32, 0.3, kv_from=0, ff=80),
                            attn(4, 2, 16, 32, 0.25), attn(4, 2, 16, 32, 0.25, kv_from=2, ff=96)],
             eps=1e-6, logit_scale=0.7)
-# heads of 64: the tensor-core prefill kernel and the one-chunk decode kernel; one KV head
+# heads of 64: the tensor-core prefill kernel and the one-chunk decode kernel; one KV head;
+# two layers read the same layer's keys and values
 ZB = config(128, 300, 700, [attn(4, 1, 64, 64, 0.11, ff=200), attn(4, 1, 64, 64, 0.13, ff=136),
-                            attn(4, 1, 64, 64, 0.13, kv_from=1, ff=200)], eps=1e-5, logit_scale=1.0)
+                            attn(4, 1, 64, 64, 0.13, kv_from=1, ff=200), attn(4, 1, 64, 64, 0.2, kv_from=1)],
+            eps=1e-5, logit_scale=1.0)
 # heads of 128, as many KV heads as heads: the decode kernel that makes q, k and v itself
 ZC = config(96, 211, 1100, [attn(2, 2, 128, 128, 0.08, ff=136), attn(2, 2, 128, 128, 0.08, kv_from=0, ff=72)],
             eps=3e-6, logit_scale=1.9)
