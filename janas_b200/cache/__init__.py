@@ -35,14 +35,17 @@ def _call(method: str, **args):
 @dataclass(frozen=True)
 class KVSpec:
     """What a mixer needs stored per position.  ``window`` 0: every position
-    stays; otherwise only the last ``window`` positions can be read again."""
+    stays; otherwise only the last ``window`` positions can be read again.
+    ``v_head_dim``: the values' head size where it is not the keys' (0: the same)."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
 
     def to_json(self):
-        return {"num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "window": self.window}
+        return {"num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "window": self.window,
+                "v_head_dim": self.v_head_dim}
 
 
 @dataclass(frozen=True)
@@ -160,7 +163,9 @@ class KVGroup:
     def __init__(self, cache: "Cache", index: int, info: dict):
         self._cache = cache
         self.index_in_cache = index
-        self.spec = KVSpec(info["num_kv_heads"], info["head_dim"], info["window"])
+        v = info.get("v_head_dim", 0)
+        self.spec = KVSpec(info["num_kv_heads"], info["head_dim"], info["window"],
+                           0 if v == info["head_dim"] else v)
         self.entries: List[int] = list(info["entries"])
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.pool = _GroupPool(self)

@@ -201,3 +201,12 @@ def test_truncate_with_a_state_of_fixed_size_goes_back_to_nothing_only():
     assert float(c.mixer_state[1][s].abs().sum()) == 0.0      # as for a new sequence
     c.free_sequence(s)
     c.check()
+
+
+def test_values_with_a_head_size_of_their_own():
+    """A group's V storage has its own head size, and groups are told apart by it."""
+    from janas_b200.cache import Cache, KVSpec
+    c = Cache([KVSpec(2, 16, 0, 32), KVSpec(2, 16), None, KVSpec(2, 16, 0, 32)], max_tokens=256, max_seqs=2)
+    assert len(c.groups) == 2
+    assert c.groups[0].entries == [0, 3] and c.groups[0].spec.v_head_dim == 32
+    assert c.groups[1].entries == [1] and c.groups[1].spec.v_head_dim == 0
