@@ -228,7 +228,7 @@ def test_sink_attention_plain_kernel(dtype, hd, vd, nh, nkv):
     close(got, want, dtype)
 
 
-@pytest.mark.parametrize("hd,nh,nkv", [(64, 4, 1), (64, 6, 3), (128, 2, 2), (128, 8, 2), (128, 40, 2)])
+@pytest.mark.parametrize("hd,nh,nkv", [(64, 4, 1), (64, 10, 5), (128, 2, 2), (128, 8, 2), (128, 40, 2)])
 def test_sink_attention_tensor_core_kernels(hd, nh, nkv):
     dt = torch.bfloat16
     lens = [1, 300, 131, 520]
