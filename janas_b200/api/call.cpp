@@ -231,6 +231,7 @@ LayerCache cache_from_json(const Json &j) {
     c.kv_heads = (int)j.get("kv_heads").as_int();
     c.head_dim = (int)j.get("head_dim").as_int();
     c.v_head_dim = j.has("v_head_dim") ? (int)j.get("v_head_dim").as_int() : c.head_dim;
+    if (j.has("v_ld")) c.kv.v_ld = (int)j.get("v_ld").as_int();
     c.state = ptr_of<void>(j.get("state"));
     c.state_spec.shape = longs(j.get("state_shape"));
     c.state_spec.dtype = dtype_of(j.get("state_dtype"), F32);
@@ -296,6 +297,7 @@ Json part_call(const std::string &method, const Json &a) {
                 r.set("num_kv_heads", s.num_kv_heads);
                 r.set("head_dim", s.head_dim);
                 r.set("v_head_dim", s.value_dim());
+                r.set("values_in_keys", s.values_in_keys);
                 r.set("window", s.window);
             }
         } else if (method == "part.state_spec") {
@@ -638,7 +640,8 @@ static Json dispatch(const std::string &method, const Json &a, Json *error_detai
         for (auto &s : a.get("kv_specs").items())
             kv.push_back(s.is_object() ? KVSpec{(int)s.get("num_kv_heads").as_int(), (int)s.get("head_dim").as_int(),
                                                 (int)s.get("window").as_int(),
-                                                s.has("v_head_dim") ? (int)s.get("v_head_dim").as_int() : 0}
+                                                s.has("v_head_dim") ? (int)s.get("v_head_dim").as_int() : 0,
+                                                s.has("values_in_keys") && s.get("values_in_keys").as_bool()}
                                        : KVSpec());
         std::vector<StateSpec> st;
         for (auto &s : a.get("state_specs").items()) {

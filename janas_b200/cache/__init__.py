@@ -36,16 +36,19 @@ def _call(method: str, **args):
 class KVSpec:
     """What a mixer needs stored per position.  ``window`` 0: every position
     stays; otherwise only the last ``window`` positions can be read again.
-    ``v_head_dim``: the values' head size where it is not the keys' (0: the same)."""
+    ``v_head_dim``: the values' head size where it is not the keys' (0: the same).
+    ``values_in_keys``: the values are the first ``v_head_dim`` entries of the keys'
+    rows (a latent that is key and value at once); the group has no V tensor."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    values_in_keys: bool = False
 
     def to_json(self):
         return {"num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "window": self.window,
-                "v_head_dim": self.v_head_dim}
+                "v_head_dim": self.v_head_dim, "values_in_keys": self.values_in_keys}
 
 
 @dataclass(frozen=True)
@@ -165,7 +168,7 @@ class KVGroup:
         self.index_in_cache = index
         v = info.get("v_head_dim", 0)
         self.spec = KVSpec(info["num_kv_heads"], info["head_dim"], info["window"],
-                           0 if v == info["head_dim"] else v)
+                           0 if v == info["head_dim"] else v, bool(info.get("values_in_keys", False)))
         self.entries: List[int] = list(info["entries"])
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.pool = _GroupPool(self)

@@ -159,10 +159,16 @@ Cache::Cache(const std::vector<KVSpec> &kv_specs, const std::vector<StateSpec> &
                                         g.first.head_dim};
         std::vector<long long> v_shape = shape;
         v_shape.back() = g.first.value_dim();
+        if (g.first.values_in_keys) {
+            if (g.first.value_dim() > g.first.head_dim)
+                fail(JB_LLM_EINVAL, "a cache group whose values lie in its keys' rows needs values no longer "
+                                    "than the keys");
+            v_shape.clear();      // no tensor of their own
+        }
         if (dev) {
             dev->make_current();
             grp->k = dev->tensor(dt, shape, true);
-            grp->v = dev->tensor(dt, v_shape, true);
+            if (!g.first.values_in_keys) grp->v = dev->tensor(dt, v_shape, true);
         } else {
             grp->k.shape = shape;
             grp->v.shape = v_shape;
@@ -352,6 +358,7 @@ size_t Cache::bytes() const {
         size_t nv = n;
         for (auto s : g->k.shape) n *= (size_t)s;
         for (auto s : g->v.shape) nv *= (size_t)s;
+        if (g->v.shape.empty()) nv = 0;      // the values lie in the keys' rows
         b += n + nv;
     }
     return b;
@@ -390,6 +397,7 @@ Json Cache::describe() const {
         j.set("num_kv_heads", g->spec.num_kv_heads);
         j.set("head_dim", g->spec.head_dim);
         j.set("v_head_dim", g->spec.value_dim());
+        j.set("values_in_keys", g->spec.values_in_keys);
         j.set("window", g->spec.window);
         Json es = Json::array();
         for (int e : g->entries) es.push(e);
@@ -400,7 +408,7 @@ Json Cache::describe() const {
         j.set("n_pages", g->pool.n_pages());
         j.set("free_pages", g->pool.n_free());
         j.set("k", (unsigned long long)(uintptr_t)g->k.ptr);
-        j.set("v", (unsigned long long)(uintptr_t)g->v.ptr);
+        j.set("v", (unsigned long long)(uintptr_t)(g->spec.values_in_keys ? g->k.ptr : g->v.ptr));
         gs.push(j);
     }
     o.set("groups", gs);

@@ -88,11 +88,14 @@ private:
 struct KVSpec {
     int num_kv_heads = 0, head_dim = 0, window = 0;
     int v_head_dim = 0;     // the values' head size where it is not the keys'; 0: the same
+    // The values are the first v_head_dim entries of the keys' rows (a latent that is
+    // key and value at once): the group then has no V tensor.
+    bool values_in_keys = false;
     bool none() const { return num_kv_heads == 0; }
     int value_dim() const { return v_head_dim > 0 ? v_head_dim : head_dim; }
     bool operator==(const KVSpec &o) const {
         return num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && window == o.window &&
-               value_dim() == o.value_dim();
+               value_dim() == o.value_dim() && values_in_keys == o.values_in_keys;
     }
 };
 
@@ -120,7 +123,9 @@ public:
     size_t entry_bytes() const;            // bytes of one entry's K
     size_t v_entry_bytes() const;          // bytes of one entry's V
     void *k_of(int entry) const { return (char *)k.ptr + (size_t)index.at(entry) * entry_bytes(); }
-    void *v_of(int entry) const { return (char *)v.ptr + (size_t)index.at(entry) * v_entry_bytes(); }
+    void *v_of(int entry) const {
+        return spec.values_in_keys ? k_of(entry) : (char *)v.ptr + (size_t)index.at(entry) * v_entry_bytes();
+    }
     int first_needed_page(long long next_pos) const;
     void extend(int slot, long long end);
     void release_unseen(int slot, long long next_pos);

@@ -130,6 +130,8 @@ class RunEntry:
 
     layer: int
     cache_of: Optional[int] = None
+    # before this entry the embedding output is added to the residual stream once more
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -147,13 +149,17 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     position_table_name: str = ""      # a table of learned position vectors; "": none
     logit_scale: float = 1.0
+    embedding_norm: Optional[PartSpec] = None      # a norm on the embedding rows
+    embedding_norm_name: str = "model.embed_norm"
 
     def to_json(self) -> Dict[str, Any]:
         d = {
             "architecture": self.architecture, "hidden_size": self.hidden_size,
             "vocab_size": self.vocab_size, "max_positions": self.max_positions,
             "layers": [l.to_json() for l in self.layers],
-            "run_order": [{"layer": e.layer, "cache_of": e.cache_of} for e in self.run_order],
+            "run_order": [dict({"layer": e.layer, "cache_of": e.cache_of},
+                               **({"add_embedding": True} if e.add_embedding else {}))
+                          for e in self.run_order],
             "final_norm": self.final_norm.to_json(), "tie_embeddings": self.tie_embeddings,
             "embedding_name": self.embedding_name, "final_norm_name": self.final_norm_name,
             "head_name": self.head_name}
@@ -161,6 +167,9 @@ class ModelSpec:
             d["position_table_name"] = self.position_table_name
         if self.logit_scale != 1.0:
             d["logit_scale"] = self.logit_scale
+        if self.embedding_norm:
+            d["embedding_norm"] = self.embedding_norm.to_json()
+            d["embedding_norm_name"] = self.embedding_norm_name
         return d
 
     @staticmethod
@@ -169,9 +178,12 @@ class ModelSpec:
         return ModelSpec(
             position_table_name=d.get("position_table_name", ""),
             logit_scale=d.get("logit_scale", 1.0),
+            embedding_norm=PartSpec.from_json(d["embedding_norm"]) if d.get("embedding_norm") else None,
+            embedding_norm_name=d.get("embedding_norm_name", "model.embed_norm"),
             architecture=d["architecture"], hidden_size=d["hidden_size"],
             vocab_size=d["vocab_size"], max_positions=d["max_positions"], layers=layers,
-            run_order=tuple(RunEntry(e["layer"], e["cache_of"]) for e in d["run_order"]),
+            run_order=tuple(RunEntry(e["layer"], e["cache_of"], bool(e.get("add_embedding", False)))
+                            for e in d["run_order"]),
             final_norm=PartSpec.from_json(d["final_norm"]), tie_embeddings=d["tie_embeddings"],
             embedding_name=d["embedding_name"], final_norm_name=d["final_norm_name"],
             head_name=d["head_name"])
@@ -241,8 +253,41 @@ class ZuzelornConfig:
         return hash(json.dumps(self.to_dict(), sort_keys=True))
 
 
+@dataclass(frozen=True)
+class DunavikConfig:
+    """The Dunavik decoder's ``config.json`` keys, as the library read them."""
+    vocab: int
+    width: int
+    norm_eps: float
+    residual_mult: float
+    loop: Mapping[str, int]                   # start, stop, times
+    layers: Tuple[Mapping[str, Any], ...]     # each: type, mixer {...}, mlp {...} or None
+    eos_token_ids: Tuple[int, ...] = ()
+    architecture: str = "Dunavik"
+    _json: Mapping[str, Any] = field(default_factory=dict, compare=False, repr=False)
+    _spec: Mapping[str, Any] = field(default_factory=dict, compare=False, repr=False)
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "DunavikConfig":
+        return _wrap(_call("config.parse", config=dict(d)))
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dict(self._json)
+
+    def to_model_spec(self) -> ModelSpec:
+        return ModelSpec.from_json(self._spec)
+
+    def __hash__(self) -> int:
+        return hash(json.dumps(self.to_dict(), sort_keys=True))
+
+
 def _wrap(r: Mapping[str, Any]):
     c = r["config"]
+    if r["architecture"] == "Dunavik":
+        return DunavikConfig(
+            vocab=c["vocab"], width=c["width"], norm_eps=c["norm"]["eps"],
+            residual_mult=c["residual_mult"], loop=dict(c["loop"]), layers=tuple(c["layers"]),
+            eos_token_ids=tuple(r["eos_token_ids"]), _json=c, _spec=r["spec"])
     if r["architecture"] == "Zuzelorn":
         return ZuzelornConfig(
             vocab=c["vocab"], width=c["width"], max_positions=c["max_positions"],
@@ -278,4 +323,4 @@ def config_from_dir(model_dir: str):
 
 
 __all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config",
-           "ZuzelornConfig", "config_from_dict", "config_from_dir", "known_architectures"]
+           "ZuzelornConfig", "DunavikConfig", "config_from_dict", "config_from_dir", "known_architectures"]

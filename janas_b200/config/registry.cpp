@@ -35,6 +35,7 @@ static Tables &ready() {
     std::call_once(once, [] {
         register_qwen3();
         register_zuzelorn();
+        register_dunavik();
     });
     return raw_tables();
 }

@@ -48,8 +48,8 @@ void ModelSpec::validate() const {
         config_error("hidden_size, vocab_size and max_positions must be positive");
     if (layers.empty()) config_error("a model needs at least one layer");
     for (size_t i = 0; i < layers.size(); i++)
-        if (layers[i].feed_forward.kind.empty() != layers[i].ffn_norm.kind.empty())
-            config_error(fmt("layer %zu: a feed-forward and its norm come together or not at all", i));
+        if (layers[i].feed_forward.kind.empty() && !layers[i].ffn_norm.kind.empty())
+            config_error(fmt("layer %zu: a norm for a feed-forward that the layer does not have", i));
     if (run_order.empty()) config_error("the run order is empty");
     for (size_t at = 0; at < run_order.size(); at++) {
         const RunEntry &e = run_order[at];
@@ -99,10 +99,15 @@ Json ModelSpec::to_json() const {
         Json o = Json::object();
         o.set("layer", e.layer);
         o.set("cache_of", e.cache_of >= 0 ? Json(e.cache_of) : Json());
+        if (e.add_embedding) o.set("add_embedding", true);
         ro.push(o);
     }
     j.set("run_order", ro);
     j.set("final_norm", final_norm.to_json());
+    if (!embedding_norm.kind.empty()) {
+        j.set("embedding_norm", embedding_norm.to_json());
+        j.set("embedding_norm_name", embedding_norm_name);
+    }
     j.set("tie_embeddings", tie_embeddings);
     if (!position_table_name.empty()) j.set("position_table_name", position_table_name);
     if (logit_scale != 1.0) j.set("logit_scale", logit_scale);
@@ -152,9 +157,12 @@ ModelSpec ModelSpec::from_json(const Json &j) {
         RunEntry e;
         e.layer = (int)o.get("layer").as_int();
         e.cache_of = o.get("cache_of").is_null() ? -1 : (int)o.get("cache_of").as_int();
+        e.add_embedding = o.get("add_embedding").is_bool() && o.get("add_embedding").as_bool();
         s.run_order.push_back(e);
     }
     s.final_norm = PartSpec::from_json(j.get("final_norm"));
+    s.embedding_norm = part_or_none(j.get("embedding_norm"));
+    s.embedding_norm_name = str_or(j, "embedding_norm_name", s.embedding_norm_name);
     s.tie_embeddings = j.get("tie_embeddings").as_bool();
     s.position_table_name = str_or(j, "position_table_name", "");
     if (j.get("logit_scale").is_number()) s.logit_scale = j.get("logit_scale").as_double();

@@ -72,9 +72,14 @@ struct LayerSpec {
 // by several entries; every entry is a place of its own in the cache.  With
 // cache_of >= 0 (the index of an earlier entry) the entry's mixer writes nothing
 // and reads that entry's cache.
+//
+// add_embedding: before this entry runs, the embedding output (the residual stream
+// as it was before the first entry) is added to the residual stream once more: the
+// start of a repeated pass over layers that have run already.
 struct RunEntry {
     int layer = 0;
     int cache_of = -1;
+    bool add_embedding = false;
 };
 
 struct ModelSpec {
@@ -83,6 +88,9 @@ struct ModelSpec {
     std::vector<LayerSpec> layers;
     std::vector<RunEntry> run_order;
     PartSpec final_norm;
+    // a norm on the embedding rows before the first layer (kind "": none)
+    PartSpec embedding_norm;
+    std::string embedding_norm_name = "model.embed_norm";
     bool tie_embeddings = false;
     // a table [max_positions, hidden] of learned position vectors added to the
     // embedding rows ("" for none), and a factor on the logits

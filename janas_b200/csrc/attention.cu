@@ -83,7 +83,8 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
                     const int32_t *__restrict__ row_seq, const int32_t *__restrict__ block_table,
                     int bt_stride, float *__restrict__ part, int row0, int n_rows, int nh, int nkv,
                     int hd, int vd, int window, float scale,
-                    const float *__restrict__ head_scale, int max_chunks)
+                    const float *__restrict__ head_scale, int max_chunks, int v_ld, float softcap,
+                    const float *__restrict__ slopes)
 {
     constexpr int KPW = 32 / LPK;
     pdl_trigger();
@@ -111,7 +112,7 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
     // a lane's 16 values of the keys (and q) and of the values; heads that are no
     // multiple of 16 are read value by value
     bool has_dims = cidx * 16 < hd, has_vals = cidx * 16 < vd;
-    bool vec_k = hd % 16 == 0, vec_v = vd % 16 == 0;
+    bool vec_k = hd % 16 == 0, vec_v = vd % 16 == 0 && v_ld % 16 == 0;
     int cnt_k = min(16, hd - cidx * 16), cnt_v = min(16, vd - cidx * 16);
     const int32_t *bt = block_table + (size_t)row_seq[row] * bt_stride;
 
@@ -136,6 +137,12 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
 #pragma unroll
     for (int g = 0; g < ATT_GT; g++)
         hs[g] = head_scale != nullptr && g < gt ? head_scale[h0 + g] : 1.0f;
+    // a head's slope: slope * distance is taken off the score of a key that far back
+    float sl[ATT_GT];
+#pragma unroll
+    for (int g = 0; g < ATT_GT; g++)
+        sl[g] = slopes != nullptr && g < gt ? slopes[h0 + g] : 0.0f;
+    float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
 
     for (int base = t0; base <= t1; base += KPW) {
         int t = base + ks;
@@ -168,12 +175,16 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
             s[g] = d * scale;
             if (head_scale != nullptr)
                 s[g] *= hs[g];
+            if (softcap > 0.0f)
+                s[g] = softcap * tanhf(s[g] * inv_cap);
+            if (slopes != nullptr)
+                s[g] -= sl[g] * (float)(pos - t);
         }
         if (valid && has_vals) {
             if (vec_v)
-                load16<T>(v_cache + at * vd + cidx * 16, kv);
+                load16<T>(v_cache + at * v_ld + cidx * 16, kv);
             else
-                load_some<T>(v_cache + at * vd + cidx * 16, kv, cnt_v);
+                load_some<T>(v_cache + at * v_ld + cidx * 16, kv, cnt_v);
         } else if (valid) {
 #pragma unroll
             for (int j = 0; j < 16; j++)
@@ -271,7 +282,8 @@ template <typename T>
 __global__ void attn_merge_kernel(const float *__restrict__ part,
                                   const int32_t *__restrict__ row_pos, T *__restrict__ out,
                                   int row0, int nh, int hd, int window, int max_chunks,
-                                  int chunks_per_part, const float *__restrict__ sink)
+                                  int chunks_per_part, const float *__restrict__ sink,
+                                  long long head_major_rows)
 {
     pdl_trigger();
     pdl_wait();
@@ -302,7 +314,10 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
         l = fmaf(l, a, expf(sk - mn));
         o *= a;
     }
-    if (d < hd)
+    // head_major_rows > 0: out is [nh, that many rows, hd], one head's rows together
+    if (d < hd && head_major_rows > 0)
+        out[((size_t)h * head_major_rows + row) * hd + d] = from_f<T>(o / l);
+    else if (d < hd)
         out[((size_t)row * nh + h) * hd + d] = from_f<T>(o / l);
 }
 
@@ -311,7 +326,8 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
                            const int32_t *row_seq, const int32_t *block_table, int bt_stride,
                            float *part, T *out, int row0, int n_rows, int nh, int nkv, int hd,
                            int vd, int window, float scale, const float *head_scale,
-                           const float *sink, int max_chunks, cudaStream_t st)
+                           const float *sink, int max_chunks, int v_ld, float softcap,
+                           const float *slopes, long long head_major_rows, cudaStream_t st)
 {
     int lpk = 1;
     while (lpk * 16 < max(hd, vd))
@@ -322,7 +338,7 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
 #define JB_ATT(L)                                                                            \
     launch(attn_partial_kernel<T, L>, grid, 128, 0, st, q, k_cache, v_cache, row_pos, row_seq, \
            block_table, bt_stride, part, row0, n_rows, nh, nkv, hd, vd, window, scale,        \
-           head_scale, max_chunks)
+           head_scale, max_chunks, v_ld, softcap, slopes)
     switch (lpk) {
     case 1: JB_ATT(1); break;
     case 2: JB_ATT(2); break;
@@ -336,7 +352,7 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
     if (cudaGetLastError() != cudaSuccess)
         return JB_ELAUNCH;
     launch(attn_merge_kernel<T>, dim3(n_rows, nh), (vd + 31) / 32 * 32, 0, st, (const float *)part,
-           row_pos, out, row0, nh, vd, window, max_chunks, 1, sink);
+           row_pos, out, row0, nh, vd, window, max_chunks, 1, sink, head_major_rows);
     return launch_status();
 }
 
@@ -380,21 +396,45 @@ extern "C" int jb_attention_sink(const void *q, const void *k_cache, const void 
                                  int window, float scale, const float *head_scale,
                                  const float *sink, int max_chunks, cudaStream_t st)
 {
+    return jb_attention_ext(q, k_cache, v_cache, dt, row_pos, row_seq, block_table, bt_stride, scratch,
+                            out, row0, n_rows, nh, nkv, hd, vd, window, scale, head_scale, sink,
+                            max_chunks, 0, 0.0f, nullptr, 0, st);
+}
+
+// The same with more of what mixers ask for.  v_ld (0: vd): the length of a row of
+// v_cache, for values that are the first vd entries of longer rows (a latent that is
+// key and value at once: v_cache is then k_cache).  softcap > 0: a score s becomes
+// softcap * tanh(s / softcap).  slopes (float [nh], or null): slopes[h] * (the row's
+// position - the key's) is taken off the score, after the cap.  head_major_rows > 0:
+// out is [nh, head_major_rows, vd], the rows of one head together.
+extern "C" int jb_attention_ext(const void *q, const void *k_cache, const void *v_cache, int dt,
+                                const int32_t *row_pos, const int32_t *row_seq,
+                                const int32_t *block_table, int bt_stride, float *scratch,
+                                void *out, int row0, int n_rows, int nh, int nkv, int hd, int vd,
+                                int window, float scale, const float *head_scale,
+                                const float *sink, int max_chunks, int v_ld, float softcap,
+                                const float *slopes, long long head_major_rows, cudaStream_t st)
+{
     if (n_rows <= 0)
         return JB_OK;
+    if (v_ld == 0)
+        v_ld = vd;
     if (hd > 512 || hd <= 0 || vd > 512 || vd <= 0 || nkv <= 0 || nh % nkv || max_chunks <= 0 ||
-        nkv > 65535 || nh > 65535)
+        nkv > 65535 || nh > 65535 || v_ld < vd || softcap < 0.0f ||
+        (head_major_rows > 0 && head_major_rows < (long long)row0 + n_rows))
         return JB_EINVAL;
     if (dt == JB_F32)
         return attention_typed<float>((const float *)q, (const float *)k_cache,
                                       (const float *)v_cache, row_pos, row_seq, block_table,
                                       bt_stride, scratch, (float *)out, row0, n_rows, nh, nkv, hd,
-                                      vd, window, scale, head_scale, sink, max_chunks, st);
+                                      vd, window, scale, head_scale, sink, max_chunks, v_ld, softcap,
+                                      slopes, head_major_rows, st);
     if (dt == JB_BF16)
         return attention_typed<bf16>((const bf16 *)q, (const bf16 *)k_cache,
                                      (const bf16 *)v_cache, row_pos, row_seq, block_table,
                                      bt_stride, scratch, (bf16 *)out, row0, n_rows, nh, nkv, hd,
-                                     vd, window, scale, head_scale, sink, max_chunks, st);
+                                     vd, window, scale, head_scale, sink, max_chunks, v_ld, softcap,
+                                     slopes, head_major_rows, st);
     return JB_EINVAL;
 }
 
@@ -424,10 +464,10 @@ extern "C" int jb_attention_merge_sink(const float *scratch, const int32_t *row_
     int threads = (hd + 31) / 32 * 32;
     if (dt == JB_F32)
         launch(attn_merge_kernel<float>, grid, threads, 0, st, scratch, row_pos, (float *)out, row0,
-               nh, hd, window, max_parts, chunks_per_part, sink);
+               nh, hd, window, max_parts, chunks_per_part, sink, 0ll);
     else if (dt == JB_BF16)
         launch(attn_merge_kernel<bf16>, grid, threads, 0, st, scratch, row_pos, (bf16 *)out, row0,
-               nh, hd, window, max_parts, chunks_per_part, sink);
+               nh, hd, window, max_parts, chunks_per_part, sink, 0ll);
     else
         return JB_EINVAL;
     return launch_status();

@@ -419,8 +419,16 @@ __global__ void add_bias_kernel(float *__restrict__ y, const float *__restrict__
     y[i] += b;
 }
 
+// A factor on the queries that grows with the position p in steps of `every`
+// positions: 1 + coef * ln(floor((p + 1) / every) + 1).
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every)
+{
+    return 1.0f + coef * logf((float)((pos + 1) / every) + 1.0f);
+}
+
 // The fused [q | k | v] product's sums plus its bias: q rows out, K and V into the
-// cache pages at each row's position.  Widths: nh hd, nkv hd, nkv vd; without
+// cache pages at each row's position.  With q_every > 0 the queries are multiplied
+// by query_temperature() of their row's position.  Widths: nh hd, nkv hd, nkv vd; without
 // `append` the product holds q alone.
 template <typename TC>
 __global__ void qkv_bias_append_kernel(const float *__restrict__ qkv, int S, size_t stride, int ld,
@@ -430,7 +438,7 @@ __global__ void qkv_bias_append_kernel(const float *__restrict__ qkv, int S, siz
                                        const int32_t *__restrict__ block_table, int bt_stride,
                                        TC *__restrict__ q_out, TC *__restrict__ k_cache,
                                        TC *__restrict__ v_cache, int nh, int nkv, int hd, int vd,
-                                       int width, size_t total)
+                                       int width, size_t total, float q_coef, int q_every)
 {
     pdl_trigger();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -443,6 +451,8 @@ __global__ void qkv_bias_append_kernel(const float *__restrict__ qkv, int S, siz
     float v = add_partials(0.0f, qkv + row * ld + c, S, stride) + bv;
     int qw = nh * hd, kw = nkv * hd;
     if (c < qw) {
+        if (q_every > 0)
+            v *= query_temperature(row_pos[row], q_coef, q_every);
         q_out[row * qw + c] = from_f<TC>(v);
         return;
     }
@@ -468,7 +478,7 @@ qkv_bias_append_vec_kernel(const float *__restrict__ qkv, int S, size_t stride, 
                            const int32_t *__restrict__ block_table, int bt_stride,
                            TC *__restrict__ q_out, TC *__restrict__ k_cache,
                            TC *__restrict__ v_cache, int nh, int nkv, int hd, int vd, int width,
-                           int n)
+                           int n, float q_coef, int q_every)
 {
     pdl_trigger();
     size_t row0 = (size_t)blockIdx.x * ROWS;
@@ -494,6 +504,8 @@ qkv_bias_append_vec_kernel(const float *__restrict__ qkv, int S, size_t stride, 
         if (!is_q && row0 + r < (size_t)n) {
             pos[r] = row_pos[row0 + r];
             page[r] = block_table[(size_t)row_seq[row0 + r] * bt_stride + pos[r] / PAGE];
+        } else if (q_every > 0 && row0 + r < (size_t)n) {
+            pos[r] = row_pos[row0 + r];
         }
     }
     pdl_wait();
@@ -508,6 +520,10 @@ qkv_bias_append_vec_kernel(const float *__restrict__ qkv, int S, size_t stride, 
         if (row >= (size_t)n)
             break;
         float4 o = add4(v[r], bv);
+        if (is_q && q_every > 0) {
+            float t = query_temperature(pos[r], q_coef, q_every);
+            o = make_float4(o.x * t, o.y * t, o.z * t, o.w * t);
+        }
         if (is_q)
             store4(q_out + row * qw + c, o);
         else if (is_k)
@@ -735,6 +751,20 @@ extern "C" int jb_qkv_bias_append(const float *qkv, int S, long long stride, int
                                   int cache_dt, int n, int nh, int nkv, int hd, int vd, int append,
                                   cudaStream_t st)
 {
+    return jb_qkv_bias_append_temp(qkv, S, stride, ld, bias, row_pos, row_seq, block_table, bt_stride,
+                                   q_out, k_cache, v_cache, cache_dt, n, nh, nkv, hd, vd, append,
+                                   0.0f, 0, st);
+}
+
+// The same with a query temperature: with q_every > 0 every query value of a row at
+// position p is multiplied by 1 + q_coef * ln(floor((p + 1) / q_every) + 1).
+extern "C" int jb_qkv_bias_append_temp(const float *qkv, int S, long long stride, int ld,
+                                       const float *bias, const int32_t *row_pos,
+                                       const int32_t *row_seq, const int32_t *block_table,
+                                       int bt_stride, void *q_out, void *k_cache, void *v_cache,
+                                       int cache_dt, int n, int nh, int nkv, int hd, int vd,
+                                       int append, float q_coef, int q_every, cudaStream_t st)
+{
     if (n <= 0)
         return JB_OK;
     if (nh <= 0 || hd <= 0 || (append && (nkv <= 0 || vd <= 0 || !k_cache || !v_cache)))
@@ -754,7 +784,7 @@ extern "C" int jb_qkv_bias_append(const float *qkv, int S, long long stride, int
 #define JB_APP(TC, R)                                                                         \
     launch(qkv_bias_append_vec_kernel<TC, R>, grid, threads, 0, st, qkv, S, (size_t)stride, ld, \
            bias, row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache,         \
-           (TC *)v_cache, nh, nkv, hd, vd, width, n)
+           (TC *)v_cache, nh, nkv, hd, vd, width, n, q_coef, q_every)
         if (cache_dt == JB_F32 && rows_per == 2)
             JB_APP(float, 2);
         else if (cache_dt == JB_F32)
@@ -770,11 +800,11 @@ extern "C" int jb_qkv_bias_append(const float *qkv, int S, long long stride, int
     if (cache_dt == JB_F32)
         launch(qkv_bias_append_kernel<float>, blocks, 256, 0, st, qkv, S, (size_t)stride, ld, bias,
                row_pos, row_seq, block_table, bt_stride, (float *)q_out, (float *)k_cache,
-               (float *)v_cache, nh, nkv, hd, vd, width, total);
+               (float *)v_cache, nh, nkv, hd, vd, width, total, q_coef, q_every);
     else if (cache_dt == JB_BF16)
         launch(qkv_bias_append_kernel<bf16>, blocks, 256, 0, st, qkv, S, (size_t)stride, ld, bias,
                row_pos, row_seq, block_table, bt_stride, (bf16 *)q_out, (bf16 *)k_cache,
-               (bf16 *)v_cache, nh, nkv, hd, vd, width, total);
+               (bf16 *)v_cache, nh, nkv, hd, vd, width, total, q_coef, q_every);
     else
         return JB_EINVAL;
     return launch_status();

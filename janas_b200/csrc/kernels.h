@@ -20,6 +20,11 @@
 #define JB_F32 0
 #define JB_BF16 1
 
+// activations of jb_activation
+#define JB_ACT_RELU2 0
+#define JB_ACT_RELU 1
+#define JB_ACT_GELU_TANH 2
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -80,6 +85,36 @@ int jb_qkv_bias_append(const float *qkv, int S, long long stride, int ld, const 
                        const int32_t *row_pos, const int32_t *row_seq, const int32_t *block_table,
                        int bt_stride, void *q_out, void *k_cache, void *v_cache, int cache_dt,
                        int n, int nh, int nkv, int hd, int vd, int append, cudaStream_t st);
+int jb_qkv_bias_append_temp(const float *qkv, int S, long long stride, int ld, const float *bias,
+                            const int32_t *row_pos, const int32_t *row_seq,
+                            const int32_t *block_table, int bt_stride, void *q_out, void *k_cache,
+                            void *v_cache, int cache_dt, int n, int nh, int nkv, int hd, int vd,
+                            int append, float q_coef, int q_every, cudaStream_t st);
+int jb_attention_ext(const void *q, const void *k_cache, const void *v_cache, int dt,
+                     const int32_t *row_pos, const int32_t *row_seq, const int32_t *block_table,
+                     int bt_stride, float *scratch, void *out, int row0, int n_rows, int nh,
+                     int nkv, int hd, int vd, int window, float scale, const float *head_scale,
+                     const float *sink, int max_chunks, int v_ld, float softcap,
+                     const float *slopes, long long head_major_rows, cudaStream_t st);
+int jb_layernorm(float *x, const float *a, int Sa, long long a_stride, const float *b, int Sb,
+                 long long b_stride, float mult, const int32_t *row_idx, const float *w,
+                 const float *bias, void *out, int out_dt, int n_out, int dm, float eps,
+                 cudaStream_t st);
+int jb_latent_down(const float *P, int S, long long stride, int ld, int q_col0, int q_rank,
+                   const float *wq, int kv_col0, int kv_rank, const float *wkv, int rot_dim,
+                   const float *cs, const float *sn, int rot_half, const int32_t *row_pos,
+                   const int32_t *row_seq, const int32_t *block_table, int bt_stride, void *cq_out,
+                   void *k_cache, int cache_dt, int n, float eps, cudaStream_t st);
+int jb_latent_q_split(const float *Q, int S, long long stride, int nh, int D, int R, int C,
+                      const float *cs, const float *sn, int rot_half, const int32_t *row_pos,
+                      void *q_plain, void *q_lat, int dt, int n, cudaStream_t st);
+int jb_latent_q_join(const float *A, int S, int nh, int C, int R, void *q_lat, int dt, int n,
+                     cudaStream_t st);
+int jb_heads_gate(const float *A, int S, int nh, int Dv, const float *g, int Sg, long long g_stride,
+                  int g_ld, int g_col0, void *out, int out_dt, int n, cudaStream_t st);
+int jb_transpose_heads(const void *in, void *out, int dt, int H, int D, int C, cudaStream_t st);
+int jb_activation(const float *z, int S, long long stride, int ld, int kind, void *out, int out_dt,
+                  int n, int ff, cudaStream_t st);
 int jb_attn_tc_decode_runs(int nh, int nkv, int hd);
 int jb_attn_tc_ok(int nh, int nkv, int hd);
 int jb_attn_tc_block_positions(int nh, int nkv);

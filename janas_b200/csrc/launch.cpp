@@ -122,17 +122,120 @@ void scale_(Device &d, float *x, long long total, float s) {
 
 Buf qkv_bias_append(Device &d, const Stack &qkv, const float *bias, const int32_t *row_pos,
                     const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt,
-                    bool append) {
+                    bool append, float q_coef, int q_every) {
     long long width = (long long)g.nh * g.hd + (append ? (long long)g.nkv * (g.hd + g.value_dim()) : 0);
     if (qkv.m < width) fail(JB_LLM_EINVAL, "qkv_bias_append: the product is narrower than q, k and v");
     if (append && (!c.k || !c.v)) fail(JB_LLM_EINVAL, "qkv_bias_append: no cache to append to");
     if (append && c.dt != out_dt) fail(JB_LLM_EINVAL, "qkv_bias_append: the cache is of another type");
     Buf q = d.pool.get((size_t)qkv.n * (size_t)g.nh * (size_t)g.hd * dtype_size(out_dt));
-    check(jb_qkv_bias_append(qkv.data(), qkv.S, qkv.stride(), as_int(qkv.m, "width"), bias, row_pos, row_seq,
-                             c.block_table, c.bt_stride, q.ptr, append ? c.k : nullptr, append ? c.v : nullptr,
-                             out_dt, as_int(qkv.n, "rows"), g.nh, g.nkv, g.hd, g.value_dim(), append ? 1 : 0,
-                             d.stream), "qkv_bias_append");
+    if (q_every < 0) fail(JB_LLM_EINVAL, "qkv_bias_append: the query temperature's step must not be negative");
+    check(jb_qkv_bias_append_temp(qkv.data(), qkv.S, qkv.stride(), as_int(qkv.m, "width"), bias, row_pos,
+                                  row_seq, c.block_table, c.bt_stride, q.ptr, append ? c.k : nullptr,
+                                  append ? c.v : nullptr, out_dt, as_int(qkv.n, "rows"), g.nh, g.nkv, g.hd,
+                                  g.value_dim(), append ? 1 : 0, q_coef, q_every, d.stream),
+          "qkv_bias_append");
     return q;
+}
+
+Buf layernorm(Device &d, float *x, long long n, long long dm, const LnParams &p, DType out_dt,
+              const Stack *a, const Stack *b, float mult, const int32_t *rows, long long n_out) {
+    need_float(out_dt, "norm output");
+    if (!a && b) { a = b; b = nullptr; }
+    if (a && rows) {
+        add_scaled_(d, x, n, dm, *a, b, mult);
+        a = b = nullptr;
+    }
+    for (const Stack *s : {a, b}) {
+        if (!s) continue;
+        if (s->n != n || s->m != dm) fail(JB_LLM_EINVAL, "layernorm: a sum's shape is not x's");
+        resolve_bias(d, const_cast<Stack &>(*s));
+    }
+    long long outs = rows ? n_out : n;
+    Buf out = d.pool.get((size_t)outs * (size_t)dm * dtype_size(out_dt));
+    check(jb_layernorm(x, a ? a->data() : nullptr, a ? a->S : 0, a ? a->stride() : 0, b ? b->data() : nullptr,
+                       b ? b->S : 0, b ? b->stride() : 0, mult, rows, p.w, p.b, out.ptr, out_dt,
+                       as_int(outs, "rows"), as_int(dm, "width"), p.eps, d.stream), "layernorm");
+    return out;
+}
+
+void add_scaled_(Device &d, float *x, long long n, long long dm, const Stack &a, const Stack *b, float mult) {
+    for (const Stack *s : {&a, b}) {
+        if (!s) continue;
+        if (s->n != n || s->m != dm) fail(JB_LLM_EINVAL, "add_scaled: a sum's shape is not x's");
+        resolve_bias(d, const_cast<Stack &>(*s));
+    }
+    check(jb_layernorm(x, a.data(), a.S, a.stride(), b ? b->data() : nullptr, b ? b->S : 0,
+                       b ? b->stride() : 0, mult, nullptr, nullptr, nullptr, nullptr, 0, as_int(n, "rows"),
+                       as_int(dm, "width"), 0.0f, d.stream), "add_scaled");
+}
+
+int activation_kind(const std::string &name) {
+    if (name == "relu2") return JB_ACT_RELU2;
+    if (name == "relu") return JB_ACT_RELU;
+    if (name == "gelu_tanh") return JB_ACT_GELU_TANH;
+    return -1;
+}
+
+Buf activation(Device &d, const Stack &z, long long ff, int kind, DType out_dt) {
+    need_float(out_dt, "activation output");
+    if (ff <= 0 || ff > z.m) fail(JB_LLM_EINVAL, "activation: the product is narrower than the feed-forward");
+    Buf out = d.pool.get((size_t)z.n * (size_t)ff * dtype_size(out_dt));
+    check(jb_activation(z.data(), z.S, z.stride(), as_int(z.m, "width"), kind, out.ptr, out_dt,
+                        as_int(z.n, "rows"), as_int(ff, "width"), d.stream), "activation");
+    return out;
+}
+
+// ------------------------------------------------------------ latent attention
+Buf latent_down(Device &d, const Stack &P, long long q_col0, long long q_rank, const float *wq,
+                long long kv_col0, long long kv_rank, const float *wkv, long long rot_dim, const float *cs,
+                const float *sn, int rot_half, const int32_t *row_pos, const int32_t *row_seq,
+                const AttnCache &c, float eps, DType out_dt) {
+    if (!c.k || !c.writes) fail(JB_LLM_EINVAL, "latent_down: no cache to write the latent to");
+    if (c.dt != out_dt) fail(JB_LLM_EINVAL, "latent_down: the cache is of another type");
+    Buf cq = d.pool.get(std::max<size_t>((size_t)P.n * (size_t)q_rank * dtype_size(out_dt), 16));
+    check(jb_latent_down(P.data(), P.S, P.stride(), as_int(P.m, "width"), (int)q_col0, (int)q_rank, wq,
+                         (int)kv_col0, (int)kv_rank, wkv, (int)rot_dim, cs, sn, rot_half, row_pos, row_seq,
+                         c.block_table, c.bt_stride, cq.ptr, c.k, out_dt, as_int(P.n, "rows"), eps, d.stream),
+          "latent_down");
+    return cq;
+}
+
+Buf latent_q_split(Device &d, const Stack &Q, int nh, long long D, long long R, long long C, const float *cs,
+                   const float *sn, int rot_half, const int32_t *row_pos, void *q_lat, DType dt) {
+    if (Q.m != (long long)nh * (D + R)) fail(JB_LLM_EINVAL, "latent_q_split: the product is not heads x (plain + rotated) wide");
+    resolve_bias(d, const_cast<Stack &>(Q));
+    Buf qp = d.pool.get((size_t)nh * (size_t)Q.n * (size_t)D * dtype_size(dt));
+    check(jb_latent_q_split(Q.data(), Q.S, Q.stride(), nh, (int)D, (int)R, (int)C, cs, sn, rot_half, row_pos,
+                            qp.ptr, q_lat, dt, as_int(Q.n, "rows"), d.stream), "latent_q_split");
+    return qp;
+}
+
+void latent_q_join(Device &d, const HeadStack &A, long long R, void *q_lat, DType dt) {
+    check(jb_latent_q_join(A.data(), A.S, A.H, as_int(A.m, "width"), (int)R, q_lat, dt, as_int(A.n, "rows"),
+                           d.stream), "latent_q_join");
+}
+
+Buf heads_gate(Device &d, const HeadStack &A, const Stack &g, long long g_col0, DType out_dt) {
+    need_float(out_dt, "heads_gate output");
+    if (g && (g.n != A.n || g_col0 < 0 || g_col0 + A.H * A.m > g.m))
+        fail(JB_LLM_EINVAL, "heads_gate: the gate does not cover the heads' values");
+    Buf out = d.pool.get((size_t)A.n * (size_t)A.H * (size_t)A.m * dtype_size(out_dt));
+    check(jb_heads_gate(A.data(), A.S, A.H, as_int(A.m, "width"), g ? g.data() : nullptr, g.S, g.stride(),
+                        as_int(g.m, "width"), (int)g_col0, out.ptr, out_dt, as_int(A.n, "rows"), d.stream),
+          "heads_gate");
+    return out;
+}
+
+DevTensor transpose_heads(Device &d, const DevTensor &w, int H) {
+    need_float(w.dt, "weight");
+    if (w.shape.size() != 2 || H <= 0 || w.shape[0] % H)
+        fail(JB_LLM_EINVAL, "transpose_heads: the rows are not a multiple of the heads");
+    long long D = w.shape[0] / H, C = w.shape[1];
+    DevTensor out = d.tensor(w.dt, {(long long)H * C, D});
+    check(jb_transpose_heads(w.ptr, out.ptr, w.dt, H, as_int(D, "rows"), as_int(C, "width"), d.stream),
+          "transpose_heads");
+    d.sync();
+    return out;
 }
 
 Buf rmsnorm(Device &d, float *x, long long n, long long dm, const DevTensor &w, float eps, DType out_dt,
@@ -217,6 +320,39 @@ Stack linear(Device &d, const void *a, DType a_dt, long long n, long long k, con
     return out;
 }
 
+HeadStack linear_heads(Device &d, const void *a, DType a_dt, int H, long long n, long long k,
+                       const DevTensor &w) {
+    need_float(a_dt, "activations");
+    need_float(w.dt, "weight");
+    if (w.shape.size() != 2 || w.shape[1] != k || H <= 0 || w.shape[0] % H)
+        fail(JB_LLM_EINVAL, "linear_heads: the weight is not [heads x features, width of the activations]");
+    HeadStack out;
+    out.H = H;
+    out.n = n;
+    out.m = w.shape[0] / H;
+    int ni = as_int(n, "rows"), mi = as_int(out.m, "features"), ki = as_int(k, "width");
+    size_t a_head = (size_t)n * (size_t)k * dtype_size(a_dt), w_head = (size_t)out.m * (size_t)k * dtype_size(w.dt);
+    bool tc = n > 0 && a_dt == BF16 && w.dt == BF16;
+    for (int h = 0; h < H && tc; h++)
+        tc = jb_gemm_tc_ok((const char *)a + h * a_head, (const char *)w.ptr + h * w_head, ni, mi, ki) != 0;
+    out.S = tc ? jb_gemm_tc_splits(ni, mi, ki) : 1;
+    size_t one = (size_t)out.S * (size_t)n * (size_t)out.m;
+    out.buf = d.pool.get(std::max<size_t>((size_t)H * one * 4, 16));
+    long long need = tc ? 0 : jb_gemm_simt_scratch(ni, mi, ki);
+    Buf scratch;
+    if (need > 0) scratch = d.pool.get((size_t)need * 4);
+    for (int h = 0; h < H && n > 0; h++) {
+        const char *ah = (const char *)a + h * a_head, *wh = (const char *)w.ptr + h * w_head;
+        float *oh = out.data() + (size_t)h * one;
+        if (tc)
+            check(jb_gemm_tc(ah, wh, oh, ni, mi, ki, out.S, d.stream), "linear_heads (tcgen05)");
+        else
+            check(jb_gemm_simt(ah, a_dt, wh, w.dt, oh, ni, mi, ki, scratch.as<float>(), d.stream),
+                  "linear_heads", need > 0 ? 2 : 1);
+    }
+    return out;
+}
+
 Buf linear_swiglu(Device &d, const void *a, DType a_dt, long long n, long long k, const DevTensor &gu) {
     if (gu.shape.size() != 2 || gu.shape[1] != k)
         fail(JB_LLM_EINVAL, "linear_swiglu: the weight's rows are not as long as the activations'");
@@ -294,12 +430,13 @@ static const size_t ATT_SCRATCH_BYTES = (size_t)256 << 20;
 
 Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const AttnGeometry &g,
               const int32_t *row_pos, const int32_t *row_seq, int max_chunks, const int32_t *blocks,
-              int n_blocks, bool decode, bool force_simt) {
+              int n_blocks, bool decode, bool force_simt, bool head_major) {
     need_float(c.dt, "attention");
     int ni = as_int(n, "rows");
     int vd = g.value_dim();
     Buf out = d.pool.get((size_t)n * (size_t)g.nh * (size_t)vd * dtype_size(c.dt));
     bool tc = !force_simt && vd == g.hd && c.dt == BF16 && (decode || blocks != nullptr) &&
+              g.softcap == 0.0f && !g.slopes && !c.v_ld && !head_major &&
               attention_tc_ok(g.nh, g.nkv, g.hd) && (decode || !g.head_scale || g.head_scale_positive);
     if (tc && !decode) {
         check(jb_attn_tc_prefill_sink(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
@@ -329,9 +466,10 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
             check(jb_attention_merge_sink(scratch.as<float>(), row_pos, out.ptr, c.dt, (int)row0, cnt, g.nh,
                                           g.hd, g.window, parts, per_cta, g.sink, d.stream), "attention merge");
         } else {
-            check(jb_attention_sink(q, c.k, c.v, c.dt, row_pos, row_seq, c.block_table, c.bt_stride,
-                                    scratch.as<float>(), out.ptr, (int)row0, cnt, g.nh, g.nkv, g.hd, vd,
-                                    g.window, g.scale, g.head_scale, g.sink, max_chunks, d.stream),
+            check(jb_attention_ext(q, c.k, c.v, c.dt, row_pos, row_seq, c.block_table, c.bt_stride,
+                                   scratch.as<float>(), out.ptr, (int)row0, cnt, g.nh, g.nkv, g.hd, vd,
+                                   g.window, g.scale, g.head_scale, g.sink, max_chunks, c.v_ld, g.softcap,
+                                   g.slopes, head_major ? n : 0, d.stream),
                   "attention", 2);
         }
     }
@@ -341,7 +479,8 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
 Buf attention_decode_qkv(Device &d, const Stack &qkv, const DevTensor *q_w, const DevTensor *k_w, float eps,
                          const float *cs, const float *sn, const AttnCache &c, const AttnGeometry &g,
                          const int32_t *row_pos, const int32_t *row_seq, int max_chunks, const float *bias) {
-    if (c.dt != BF16 || !c.k || !jb_attn_tc_decode_runs(g.nh, g.nkv, g.hd) || g.value_dim() != g.hd)
+    if (c.dt != BF16 || !c.k || !jb_attn_tc_decode_runs(g.nh, g.nkv, g.hd) || g.value_dim() != g.hd ||
+        g.softcap != 0.0f || g.slopes || c.v_ld)
         return Buf();
     long long width = (long long)(g.nh + (c.writes ? 2 * g.nkv : 0)) * g.hd;
     if (qkv.m < width) fail(JB_LLM_EINVAL, "attention: qkv is narrower than the heads it holds");

@@ -13,6 +13,7 @@
 #pragma once
 
 #include <cstdint>
+#include <string>
 
 #include "../engine/device.h"
 
@@ -67,6 +68,24 @@ Buf gated_dyt_residual(Device &d, float *x, const Stack &y, const Stack &g, long
 Buf polynorm(Device &d, const Stack &z, long long ff, const float *coef, float eps, DType out_dt);
 void scale_(Device &d, float *x, long long total, float s);
 
+// Layer norm with weight and bias (float32 [dm] each; b may be null).
+struct LnParams {
+    const float *w = nullptr, *b = nullptr;
+    float eps = 0.0f;
+};
+// (x - mean) / sqrt(var + eps) * w + b on the rows of x (float32 [n, dm]).  With a
+// (and optionally b), two stacks of partial sums, x += mult * (sum a + sum b) happens
+// first, in place.  rows as in rmsnorm (the add then runs as a launch of its own).
+Buf layernorm(Device &d, float *x, long long n, long long dm, const LnParams &p, DType out_dt,
+              const Stack *a, const Stack *b, float mult, const int32_t *rows, long long n_out);
+// x += mult * (sum a + sum b) (b may be null)
+void add_scaled_(Device &d, float *x, long long n, long long dm, const Stack &a, const Stack *b, float mult);
+
+// act(sum z) over the first ff columns of z's rows; kind: "relu2" (the square of
+// relu), "relu", "gelu_tanh".  [n, ff] in out_dt.
+int activation_kind(const std::string &name);       // -1: unknown
+Buf activation(Device &d, const Stack &z, long long ff, int kind, DType out_dt);
+
 // RMSNorm of the rows of x (float32 [n, dm]).  With delta, x is first updated in
 // place, x += delta[0] + ... + delta[S-1].  With rows (n_out int32 indices on the
 // device) only those rows are normalized and returned, in that order; delta and
@@ -90,6 +109,16 @@ void rope_table(Device &d, const float *inv_freq_dev, int half, long long n_pos,
 // whole: S = 1 in every case.
 Stack linear(Device &d, const void *a, DType a_dt, long long n, long long k, const DevTensor &weight,
              bool whole = false, bool force_simt = false, int splits = 0);
+// One product per head: a [H, n, k] (one head's rows together) . w[H m, k]^T, head h
+// with rows h m .. h m + m - 1 of w.  The result: float32 [H, S, n, m].
+struct HeadStack {
+    Buf buf;
+    int H = 0, S = 0;
+    long long n = 0, m = 0;
+    float *data() const { return (float *)buf.ptr; }
+};
+HeadStack linear_heads(Device &d, const void *a, DType a_dt, int H, long long n, long long k,
+                       const DevTensor &w);
 // Into how many parts of k the tensor-core product is cut when the caller leaves it open.
 int linear_parts(long long n, long long m, long long k);
 // SiLU(a . gate^T) * (a . up^T) in one tensor-core kernel; an empty Buf when the
@@ -100,6 +129,8 @@ Buf linear_swiglu(Device &d, const void *a, DType a_dt, long long n, long long k
 struct AttnGeometry {
     int nh = 0, nkv = 0, hd = 0, window = 0;
     float scale = 1.0f;
+    float softcap = 0.0f;                    // > 0: a score s becomes softcap * tanh(s / softcap)
+    const float *slopes = nullptr;           // float32 [nh]: slope * (distance back) is taken off a score
     int vd = 0;                              // the values' head size; 0: as the keys'
     const float *head_scale = nullptr;       // float32 [nh] on the device: a factor per head on the scores
     const float *sink = nullptr;             // float32 [nh]: exp(sink) joins each softmax's denominator
@@ -115,6 +146,7 @@ struct AttnCache {
     const int32_t *block_table = nullptr;  // [sequences, bt_stride]
     int bt_stride = 0;
     bool writes = true;
+    int v_ld = 0;                          // the length of v's rows where it is not the values' head size
 };
 
 // Per-head RMSNorm of q and k (when weights are given), NeoX rotation by the rows'
@@ -132,7 +164,26 @@ Buf qk_norm_rope_append(Device &d, const Stack &qkv, const DevTensor *q_w, const
 // (a mixer that reads another's keys and values).
 Buf qkv_bias_append(Device &d, const Stack &qkv, const float *bias, const int32_t *row_pos,
                     const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt,
-                    bool append);
+                    bool append, float q_coef = 0.0f, int q_every = 0);
+
+// The element-wise steps of latent attention (csrc/latent.cu).  P: the down products'
+// sums; the RMS-normed query latent [n, q_rank] comes back in out_dt, the row
+// [RMS-normed latent | rotated shared key part] goes to the cache at each row's position.
+Buf latent_down(Device &d, const Stack &P, long long q_col0, long long q_rank, const float *wq,
+                long long kv_col0, long long kv_rank, const float *wkv, long long rot_dim,
+                const float *cos, const float *sin, int rot_half, const int32_t *row_pos,
+                const int32_t *row_seq, const AttnCache &c, float eps, DType out_dt);
+// Q: the query product's sums [S, n, nh (D + R)] -> the plain parts [nh, n, D] (returned)
+// and the rotated parts in columns C.. of q_lat [n, nh, C + R]
+Buf latent_q_split(Device &d, const Stack &Q, int nh, long long D, long long R, long long C,
+                   const float *cos, const float *sin, int rot_half, const int32_t *row_pos,
+                   void *q_lat, DType dt);
+void latent_q_join(Device &d, const HeadStack &A, long long R, void *q_lat, DType dt);
+// per-head sums joined into rows [n, H m], times sigmoid of the gate's sums (columns
+// g_col0.. of g; an empty g: no gate)
+Buf heads_gate(Device &d, const HeadStack &A, const Stack &g, long long g_col0, DType out_dt);
+// w viewed as [H, rows / H, cols] -> [H, cols, rows / H], a new tensor of the same type
+DevTensor transpose_heads(Device &d, const DevTensor &w, int H);
 
 // The blocks a prefill step is cut into for the tensor-core kernel: int32
 // [blocks, 4] = first row, positions, the first row's position, sequence;
@@ -150,7 +201,7 @@ bool attention_tc_ok(int nh, int nkv, int hd);
 // sequence) or blocks (from attention_blocks).
 Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const AttnGeometry &g,
               const int32_t *row_pos, const int32_t *row_seq, int max_chunks, const int32_t *blocks,
-              int n_blocks, bool decode, bool force_simt = false);
+              int n_blocks, bool decode, bool force_simt = false, bool head_major = false);
 
 // qk_norm_rope_append and attention(decode) in one kernel, from the q,k,v product's
 // partial sums; an empty Buf where the kernel does not take these sizes and types.

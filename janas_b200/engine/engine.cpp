@@ -169,6 +169,7 @@ std::vector<LayerCache> Engine::layer_caches(
             lc.kv_heads = g->spec.num_kv_heads;
             lc.head_dim = g->spec.head_dim;
             lc.v_head_dim = g->spec.value_dim();
+            if (g->spec.values_in_keys) lc.kv.v_ld = g->spec.head_dim;
         }
         out.push_back(lc);
     }

@@ -11,6 +11,11 @@ DecoderModel::DecoderModel(const ModelSpec &s, DType dt, Device *d) : spec(s), d
     final_norm = build_norm(spec.final_norm, dt, d);
     if (final_norm->size() != spec.hidden_size)
         config_error("the final norm's size is not the model's hidden size");
+    if (!spec.embedding_norm.kind.empty()) {
+        embedding_norm = build_norm(spec.embedding_norm, dt, d);
+        if (embedding_norm->size() != spec.hidden_size)
+            config_error("the embedding norm's size is not the model's hidden size");
+    }
 }
 
 void DecoderModel::layer_names(int i, std::string n[6]) const {
@@ -44,6 +49,7 @@ TensorList DecoderModel::top_tensors() const {
     if (!spec.position_table_name.empty())
         t.emplace_back(spec.position_table_name,
                        TensorSpec{{spec.max_positions, spec.hidden_size}, EMBEDDING, false});
+    if (embedding_norm) embedding_norm->tensors(spec.embedding_norm_name, t);
     final_norm->tensors(spec.final_norm_name, t);
     t.emplace_back(spec.head_name, TensorSpec{{spec.vocab_size, spec.hidden_size}, MATRIX, spec.tie_embeddings});
     return t;
@@ -53,6 +59,11 @@ TensorList DecoderModel::tensors() const {
     TensorList top = top_tensors();
     TensorList t;
     size_t first = spec.position_table_name.empty() ? 1 : 2;     // the tables come first
+    if (embedding_norm) {
+        TensorList en;
+        embedding_norm->tensors(spec.embedding_norm_name, en);
+        first += en.size();                                      // and the norm of their rows
+    }
     t.insert(t.end(), top.begin(), top.begin() + first);
     for (size_t i = 0; i < blocks.size(); i++) {
         TensorList l = layer_tensors((int)i);
@@ -77,6 +88,7 @@ void DecoderModel::load_top(TensorMap &t) {
     } else {
         fail(JB_LLM_EOPEN, "tensor " + spec.head_name + " is missing");
     }
+    if (embedding_norm) embedding_norm->load(spec.embedding_norm_name, t);
     final_norm->load(spec.final_norm_name, t);
 }
 
@@ -147,7 +159,7 @@ size_t DecoderModel::weight_bytes() const {
                               (const Part *)b.post_mixer_norm.get(), (const Part *)b.post_ffn_norm.get()})
             if (p) total += p->weight_bytes();
     }
-    return total + final_norm->weight_bytes();
+    return total + final_norm->weight_bytes() + (embedding_norm ? embedding_norm->weight_bytes() : 0);
 }
 
 std::vector<KVSpec> DecoderModel::kv_specs() const {
@@ -191,11 +203,31 @@ Buf DecoderModel::forward(StepContext &ctx, const int32_t *tokens, std::vector<L
     Stack pending;
     ctx.normed.reset();
     ctx.normed_by = nullptr;
+    if (embedding_norm) x = embedding_norm->apply(ctx, x.as<float>(), n, F32, nullptr, nullptr, 0);
+    // the embedding output, kept for the entries that add it once more
+    Stack again;
+    for (auto &e : spec.run_order)
+        if (e.add_embedding && !again) {
+            again.buf = d.pool.get((size_t)n * (size_t)spec.hidden_size * 4);
+            again.S = 1;
+            again.n = n;
+            again.m = spec.hidden_size;
+            cuda_check(cudaMemcpyAsync(again.buf.ptr, x.ptr, (size_t)n * (size_t)spec.hidden_size * 4,
+                                       cudaMemcpyDeviceToDevice, d.stream), "keeping the embedding output");
+        }
     for (size_t e = 0; e < spec.run_order.size(); e++) {
         Block &b = *blocks[(size_t)spec.run_order[e].layer];
+        if (spec.run_order[e].add_embedding) {
+            if (pending) {
+                ops::add_(d, x.as<float>(), n, spec.hidden_size, pending);
+                pending = Stack();
+            }
+            ops::add_(d, x.as<float>(), n, spec.hidden_size, again);
+        }
         // the norm that meets the residual stream next: the next entry's first one (the
-        // model's last norm runs on the wanted rows alone and is not computed ahead)
-        b.next_norm = e + 1 < spec.run_order.size()
+        // model's last norm runs on the wanted rows alone and is not computed ahead, and
+        // neither is a norm that something is added in front of)
+        b.next_norm = e + 1 < spec.run_order.size() && !spec.run_order[e + 1].add_embedding
                           ? blocks[(size_t)spec.run_order[e + 1].layer]->mixer_norm.get() : nullptr;
         b.forward(ctx, x.as<float>(), pending, caches[e]);
         if (ctx.trace) {

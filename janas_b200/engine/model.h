@@ -61,7 +61,7 @@ public:
     DType dtype;
     Device *dev;
     std::vector<std::unique_ptr<Block>> blocks;
-    std::unique_ptr<Norm> final_norm;
+    std::unique_ptr<Norm> final_norm, embedding_norm;
     DevTensor embedding, head, position_table;
     bool loaded = false;
 

@@ -175,8 +175,15 @@ private:
 //   s_ij = (q_i . k_j) * scale * temp_a,  j <= i  (and within the window, if any)
 //   p_ij = exp(s_ij) / (exp(sink_a) + sum_j exp(s_ij));   out = Wo concat(p v) + bo
 //
+// Further, each optional: a cap on the scores, s <- softcap * tanh(s / softcap); a
+// distance bias, slope_a * (i - j) taken off the score of key j for the query at i,
+// with slope_a = 2^(-e (a + 1) / H) for head a of H (distance_slope_exponent = e); a
+// query temperature, q_i multiplied by 1 + coef * ln(floor((i + 1) / every) + 1).
+//
 // params: hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim (default: head_dim),
-// scale (default 1/sqrt(head_dim)), window (0: none), bias, head_scale, sink, own_kv
+// scale (default 1/sqrt(head_dim)), window (0: none), softcap (0 or absent: none),
+// distance_slope_exponent (absent: no bias), q_temp_coef and q_temp_every (absent or
+// every = 0: none), bias, head_scale, sink, own_kv
 // (booleans; own_kv false: the run order gives this layer another entry's cache and it
 // has no key and value products), names (optional): q, k, v, o, bias (a suffix),
 // head_scale, sink.
@@ -194,6 +201,13 @@ public:
         head_scale_ = flag(s, "head_scale", false);
         sink_ = flag(s, "sink", false);
         own_kv_ = flag(s, "own_kv", true);
+        g_.softcap = s.has("softcap") ? (float)s.get_double("softcap") : 0.0f;
+        has_slopes_ = s.has("distance_slope_exponent");
+        slope_exponent_ = has_slopes_ ? s.get_double("distance_slope_exponent") : 0.0;
+        q_every_ = (int)s.get_int("q_temp_every", 0);
+        q_coef_ = q_every_ > 0 ? (float)s.get_double("q_temp_coef") : 0.0f;
+        if (g_.softcap < 0.0f || q_every_ < 0)
+            config_error("sink_attention: softcap and q_temp_every must not be negative");
         if (hidden_ <= 0 || g_.nh <= 0 || g_.nkv <= 0) config_error("sink_attention: sizes must be positive");
         if (g_.nh % g_.nkv) config_error("sink_attention: num_heads must be a multiple of num_kv_heads");
         if (g_.hd <= 0 || g_.hd > 512 || g_.vd <= 0 || g_.vd > 512)
@@ -249,6 +263,15 @@ public:
         if (sink_) sinks_ = take(t, name(p, n_sink_));
         w_o_ = take(t, name(p, n_o_));
         if (bias_) b_o_ = take(t, name(p, n_o_ + n_bias_));
+        if (has_slopes_) {
+            std::vector<float> sl((size_t)g_.nh);
+            for (int a = 0; a < g_.nh; a++)
+                sl[(size_t)a] = (float)std::pow(2.0, -slope_exponent_ * (double)(a + 1) / (double)g_.nh);
+            slopes_ = dev->tensor(F32, {g_.nh});
+            cuda_check(cudaMemcpy(slopes_.ptr, sl.data(), sl.size() * 4, cudaMemcpyHostToDevice),
+                       "copying the heads' slopes");
+            g_.slopes = (const float *)slopes_.ptr;
+        }
         g_.head_scale = head_scale_ ? (const float *)temp_.ptr : nullptr;
         g_.sink = sink_ ? (const float *)sinks_.ptr : nullptr;
         if (head_scale_) {
@@ -301,7 +324,7 @@ public:
         int max_chunks = (int)(ctx.max_pos / chunk_ + 1);
         if (g_.window) max_chunks = std::min(max_chunks, (g_.window - 1) / chunk_ + 2);
         bool decode = ctx.kind == DECODE;
-        if (decode && ctx.dtype == BF16) {
+        if (decode && ctx.dtype == BF16 && q_every_ == 0) {
             // one new token per sequence: the attention kernel makes q and the new key and
             // value from the product's sums and its bias itself, where it takes the sizes
             Buf a = ops::attention_decode_qkv(d, qkv, nullptr, nullptr, 0.0f, nullptr, nullptr, cache.kv, g_,
@@ -311,12 +334,14 @@ public:
                 return output(ctx, a);
             }
         }
-        Buf q = ops::qkv_bias_append(d, qkv, b_in, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype, own_kv_);
+        Buf q = ops::qkv_bias_append(d, qkv, b_in, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype, own_kv_,
+                                     q_coef_, q_every_);
         keep_side(ctx, qkv);
         const int32_t *blocks = nullptr;
         int n_blocks = 0;
         if (!decode && ctx.dtype == BF16 && ops::attention_tc_ok(g_.nh, g_.nkv, g_.hd) && g_.vd == g_.hd &&
-            (!head_scale_ || g_.head_scale_positive) && !ctx.seq_len.empty()) {
+            (!head_scale_ || g_.head_scale_positive) && !ctx.seq_len.empty() && g_.softcap == 0.0f &&
+            !has_slopes_) {
             int per = ops::attention_block_positions(g_.nh, g_.nkv);
             std::string key = "attention_blocks/" + std::to_string(per);
             auto it = ctx.extras.find(key);
@@ -363,15 +388,186 @@ private:
     long long hidden_;
     ops::AttnGeometry g_;
     bool bias_, head_scale_, sink_, own_kv_;
+    bool has_slopes_ = false;
+    double slope_exponent_ = 0.0;
+    float q_coef_ = 0.0f;
+    int q_every_ = 0;
     std::string n_q_, n_k_, n_v_, n_o_, n_bias_, n_hs_, n_sink_;
-    DevTensor w_in_, b_in_, w_o_, b_o_, temp_, sinks_;
+    DevTensor w_in_, b_in_, w_o_, b_o_, temp_, sinks_, slopes_;
     long long side_col0_ = 0, side_cols_ = 0;
+    int chunk_ = 0;
+};
+
+// Latent attention: keys and values of all heads come from one latent vector per
+// position, and one rotated key part is shared by all heads.  With H heads, per head
+// D plain and R rotated query/key values and Dv values, a latent of C values and a
+// query latent of Cq:
+//
+//   cq = rms(Wdq h) wq;  q = Wuq cq, per head [D plain | R rotated]
+//   z = Wdkv h;  c = rms(z[0:C]) wc;  kr = z[C:C+R]
+//   the first rotary_dim values of q's rotated part and of kr turn pair by pair
+//   (2i, 2i+1) with the position
+//   s_ij = (q_plain_i . (Wuk c_j)_head + q_rot_i . kr_j) * scale,  j <= i;  softmax
+//   out = Wo (concat_heads(sum_j p_ij (Wuv c_j)_head) * sigmoid(Wg h))     (the gate optional)
+//
+// The cache holds [c | kr] per position, once for all heads, and the values are read
+// from the same rows (KVSpec::values_in_keys).  Keys and values per head are never
+// formed: a head's query goes through its key matrix first (q_lat = Wuk_head^T q_plain),
+// scores and weighted sums run over the latents, and the head's value matrix is
+// applied to the weighted sum; the two per-head products are one product per head
+// over rows gathered head by head (ops::linear_heads).
+//
+// params: hidden_size, num_heads, head_dim (D), rot_dim (R), v_head_dim (Dv), kv_rank
+// (C), q_rank (Cq), scale, eps, gate (default true), position (a part, kind
+// rope_pairs), names (optional): dq, dq_norm, uq, dkv, dkv_norm, uk, uv, gate, o
+class LatentAttention : public Mixer {
+public:
+    LatentAttention(const PartSpec &s, DType dt, Device *d) : Mixer(s, dt, d) {
+        hidden_ = s.get_int("hidden_size");
+        H_ = (int)s.get_int("num_heads");
+        D_ = s.get_int("head_dim");
+        R_ = s.get_int("rot_dim");
+        Dv_ = s.get_int("v_head_dim");
+        C_ = s.get_int("kv_rank");
+        Cq_ = s.get_int("q_rank");
+        scale_ = (float)s.get_double("scale");
+        eps_ = (float)s.get_double("eps");
+        gate_ = s.has("gate") ? s.params.get("gate").as_bool() : true;
+        if (hidden_ <= 0 || H_ <= 0 || D_ <= 0 || R_ < 0 || Dv_ <= 0 || C_ <= 0 || Cq_ <= 0)
+            config_error("latent_attention: sizes must be positive");
+        if (C_ + R_ > 512)
+            config_error(fmt("latent_attention: kv_rank + rot_dim = %lld: the attention kernels take rows of "
+                             "up to 512 values", C_ + R_));
+        position_ = build_position(s.get_part("position"), dt, d);
+        if (position_->rotary_dim() > R_ || position_->rotary_dim() % 2)
+            config_error(fmt("latent_attention: %d rotated dimensions do not fit the rotated part of %lld",
+                             position_->rotary_dim(), R_));
+        const Json &nm = s.params.get("names");
+        auto leaf = [&](const char *key, const char *dflt) {
+            return nm.is_object() && nm.get(key).is_string() ? nm.get(key).as_string() : std::string(dflt);
+        };
+        n_dq_ = leaf("dq", "q_down.weight");
+        n_dqn_ = leaf("dq_norm", "q_down_norm.weight");
+        n_uq_ = leaf("uq", "q_up.weight");
+        n_dkv_ = leaf("dkv", "kv_down.weight");
+        n_dkvn_ = leaf("dkv_norm", "kv_down_norm.weight");
+        n_uk_ = leaf("uk", "k_up.weight");
+        n_uv_ = leaf("uv", "v_up.weight");
+        n_g_ = leaf("gate", "gate.weight");
+        n_o_ = leaf("o", "o_proj.weight");
+        g_.nh = H_;
+        g_.nkv = 1;
+        g_.hd = (int)(C_ + R_);
+        g_.vd = (int)C_;
+        g_.scale = scale_;
+    }
+
+    void tensors(const std::string &p, TensorList &out) const override {
+        out.emplace_back(name(p, n_dq_), TensorSpec{{Cq_, hidden_}, MATRIX, false});
+        out.emplace_back(name(p, n_dqn_), TensorSpec{{Cq_}, PARAM, false, 1.0f, 0.1f});
+        out.emplace_back(name(p, n_uq_), TensorSpec{{H_ * (D_ + R_), Cq_}, MATRIX, false});
+        out.emplace_back(name(p, n_dkv_), TensorSpec{{C_ + R_, hidden_}, MATRIX, false});
+        out.emplace_back(name(p, n_dkvn_), TensorSpec{{C_}, PARAM, false, 1.0f, 0.1f});
+        out.emplace_back(name(p, n_uk_), TensorSpec{{H_ * D_, C_}, MATRIX, false});
+        out.emplace_back(name(p, n_uv_), TensorSpec{{H_ * Dv_, C_}, MATRIX, false});
+        if (gate_) out.emplace_back(name(p, n_g_), TensorSpec{{H_ * Dv_, hidden_}, MATRIX, false});
+        out.emplace_back(name(p, n_o_), TensorSpec{{hidden_, H_ * Dv_}, MATRIX, false});
+        position_->tensors(name(p, "position"), out);
+    }
+
+    void load(const std::string &p, TensorMap &t) override {
+        // the three matrices that read the mixer's input: one product
+        std::vector<DevTensor> in = {take(t, name(p, n_dq_)), take(t, name(p, n_dkv_))};
+        if (gate_) in.push_back(take(t, name(p, n_g_)));
+        w_in_ = fuse_rows(*dev, in);
+        wq_norm_ = take(t, name(p, n_dqn_));
+        wc_norm_ = take(t, name(p, n_dkvn_));
+        w_uq_ = take(t, name(p, n_uq_));
+        {
+            // a head's query goes through its key matrix: [D, C] per head, kept as [C, D]
+            DevTensor uk = take(t, name(p, n_uk_));
+            w_ukT_ = ops::transpose_heads(*dev, uk, H_);
+        }
+        w_uv_ = take(t, name(p, n_uv_));
+        w_o_ = take(t, name(p, n_o_));
+        position_->load(name(p, "position"), t);
+    }
+
+    size_t weight_bytes() const override {
+        return w_in_.bytes() + w_uq_.bytes() + w_ukT_.bytes() + w_uv_.bytes() + w_o_.bytes() +
+               wq_norm_.bytes() + wc_norm_.bytes();
+    }
+
+    KVSpec kv_spec() const override { return KVSpec{1, (int)(C_ + R_), 0, (int)C_, true}; }
+
+    void prepare(long long n_positions) override {
+        position_->prepare(n_positions);
+        chunk_ = ops::attention_chunk();
+    }
+    bool supports(StepKind) const override { return true; }
+    bool graph_safe() const override { return true; }
+
+    Stack forward(StepContext &ctx, const void *h, LayerCache &cache) override {
+        Device &d = *ctx.dev;
+        int rot_half = position_->rotary_dim() / 2;
+        if (rot_half > 0 && ctx.max_pos >= position_->n_positions())
+            fail(JB_LLM_EINVAL, fmt("position %lld is beyond the %lld positions the encoding was prepared "
+                                    "for", ctx.max_pos, position_->n_positions()));
+        if (!cache.kv.k || !cache.kv.writes || cache.kv_heads != 1 || cache.head_dim != g_.hd ||
+            cache.v_head_dim != g_.vd || cache.kv.v_ld != g_.hd)
+            fail(JB_LLM_EINVAL, "latent_attention: the cache this layer was given does not hold its latents");
+        if (!chunk_) chunk_ = ops::attention_chunk();
+        long long n = ctx.n_rows;
+        size_t esz = dtype_size(ctx.dtype);
+        Stack P = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        Buf cq = ops::latent_down(d, P, 0, Cq_, (const float *)wq_norm_.ptr, Cq_, C_,
+                                  (const float *)wc_norm_.ptr, R_, position_->cos(), position_->sin(), rot_half,
+                                  ctx.row_pos, ctx.row_seq, cache.kv, eps_, ctx.dtype);
+        Buf q_lat = d.pool.get((size_t)n * (size_t)H_ * (size_t)(C_ + R_) * esz);
+        {
+            Stack Q = ops::linear(d, cq.ptr, ctx.dtype, n, Cq_, w_uq_);
+            Buf q_plain = ops::latent_q_split(d, Q, H_, D_, R_, C_, position_->cos(), position_->sin(), rot_half,
+                                              ctx.row_pos, q_lat.ptr, ctx.dtype);
+            ops::HeadStack A = ops::linear_heads(d, q_plain.ptr, ctx.dtype, H_, n, D_, w_ukT_);
+            ops::latent_q_join(d, A, R_, q_lat.ptr, ctx.dtype);
+        }
+        int max_chunks = (int)(ctx.max_pos / chunk_ + 1);
+        // the weighted sums of the latents, one head's rows together
+        Buf o = ops::attention(d, q_lat.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, nullptr, 0,
+                               ctx.kind == DECODE, false, true);
+        q_lat.reset();
+        ops::HeadStack V = ops::linear_heads(d, o.ptr, ctx.dtype, H_, n, C_, w_uv_);
+        Stack none;
+        Buf a = ops::heads_gate(d, V, gate_ ? P : none, Cq_ + C_ + R_, ctx.dtype);
+        return ops::linear(d, a.ptr, ctx.dtype, n, (long long)H_ * Dv_, w_o_);
+    }
+
+    Json info() const override {
+        Json o = Json::object();
+        o.set("position", position_->info());
+        o.set("position_kind", position_->spec.kind);
+        o.set("gate", gate_);
+        return o;
+    }
+
+private:
+    long long hidden_, D_, R_, Dv_, C_, Cq_;
+    int H_;
+    float scale_, eps_;
+    bool gate_;
+    ops::AttnGeometry g_;
+    std::unique_ptr<PositionEncoding> position_;
+    std::string n_dq_, n_dqn_, n_uq_, n_dkv_, n_dkvn_, n_uk_, n_uv_, n_g_, n_o_;
+    DevTensor w_in_, wq_norm_, wc_norm_, w_uq_, w_ukT_, w_uv_, w_o_;
     int chunk_ = 0;
 };
 
 }  // namespace
 
 void register_builtin_mixers() {
+    register_part("mixer", "latent_attention", [](const PartSpec &s, DType dt, Device *d) {
+        return std::unique_ptr<Part>(new LatentAttention(s, dt, d));
+    });
     register_part("mixer", "sink_attention", [](const PartSpec &s, DType dt, Device *d) {
         return std::unique_ptr<Part>(new SinkAttention(s, dt, d));
     });

@@ -2,6 +2,10 @@
 //
 // prenorm: x += mixer(norm(x)); x += ffn(norm(x))  (src/llm/model.c:743-796).
 //
+// parallel: one norm, both sublayers read its output, and their results join the
+// residual stream together, times a factor:
+//     h = norm(x);  x += m * (mixer(h) + ffn(h))       (ffn(h) = 0 for a layer without one)
+//
 // sandwich: a norm before and after each sublayer, and optionally a gate on the
 // sublayer's result, computed from the sublayer's own input:
 //     h = norm_in(x);  y = sublayer(h);  y *= sigmoid(G h + g);  x += norm_out(y)
@@ -28,6 +32,46 @@ public:
     }
 };
 
+// block_params: residual_mult (default 1): the factor m on the sublayers' sum.
+// The add is left to the norm that meets the residual stream next where the model
+// names one (Block::next_norm): its result then waits in ctx.normed.
+class ParallelBlock : public Block {
+public:
+    ParallelBlock(BlockParts p, const LayerSpec &ls) : Block(std::move(p)) {
+        if (ffn_norm || post_mixer_norm || post_ffn_norm)
+            config_error("parallel: the arrangement has one norm, before both sublayers");
+        const Json &m = ls.block_params.get("residual_mult");
+        mult_ = m.is_number() ? (float)m.as_double() : 1.0f;
+    }
+
+    void forward(StepContext &ctx, float *x, Stack &pending, LayerCache &cache) override {
+        long long n = ctx.n_rows;
+        Buf h;
+        if (ctx.normed && ctx.normed_by == mixer_norm.get()) {
+            if (pending) fail(JB_LLM_EFAIL, "parallel: a norm was computed ahead of a pending sum");
+            h = std::move(ctx.normed);
+        } else {
+            h = mixer_norm->apply(ctx, x, n, ctx.dtype, pending ? &pending : nullptr, nullptr, 0);
+        }
+        ctx.normed.reset();
+        ctx.normed_by = nullptr;
+        pending = Stack();
+        Stack y = mixer->forward(ctx, h.ptr, cache);
+        Stack z;
+        if (feed_forward) z = feed_forward->forward(ctx, h.ptr);
+        if (next_norm) {
+            ctx.normed = const_cast<Norm *>(next_norm)->apply_after_add(ctx, x, n, ctx.dtype, y,
+                                                                        z ? &z : nullptr, mult_);
+            ctx.normed_by = next_norm;
+        } else {
+            ops::add_scaled_(*ctx.dev, x, n, ctx.hidden, y, z ? &z : nullptr, mult_);
+        }
+    }
+
+private:
+    float mult_ = 1.0f;
+};
+
 // block_params: hidden_size; mixer_gate / ffn_gate: the tensor names (below the
 // layer's prefix) of the gates' matrices [hidden, hidden], absent or null for no
 // gate; gate_bias: the suffix of a gate's bias vector ("" for none); fuse (default
@@ -37,6 +81,7 @@ public:
     SandwichBlock(BlockParts p, const LayerSpec &ls, DType dt, Device *d) : Block(std::move(p)), dev_(d) {
         if (!post_mixer_norm || (feed_forward && !post_ffn_norm))
             config_error("sandwich: every sublayer needs a norm on its result");
+        if (feed_forward && !ffn_norm) config_error("sandwich: the feed-forward needs its norm");
         const Json &bp = ls.block_params;
         hidden_ = bp.get("hidden_size").is_number() ? bp.get("hidden_size").as_int() : mixer_norm->size();
         if (bp.get("mixer_gate").is_string()) gate_name_[0] = bp.get("mixer_gate").as_string();
@@ -183,6 +228,9 @@ private:
 void register_builtin_blocks() {
     register_block("prenorm", [](BlockParts p, const LayerSpec &, DType, Device *) {
         return std::unique_ptr<Block>(new PreNormBlock(std::move(p)));
+    });
+    register_block("parallel", [](BlockParts p, const LayerSpec &ls, DType, Device *) {
+        return std::unique_ptr<Block>(new ParallelBlock(std::move(p), ls));
     });
     register_block("sandwich", [](BlockParts p, const LayerSpec &ls, DType dt, Device *d) {
         return std::unique_ptr<Block>(new SandwichBlock(std::move(p), ls, dt, d));

@@ -142,9 +142,58 @@ private:
     bool side_ = false;     // the up matrix carries side rows after its own
 };
 
+// A dense feed-forward of two matrices: down(act(up(x))), no biases, the activation
+// value by value.
+// params: hidden_size, intermediate_size, activation ("relu2": the square of relu;
+// "relu"; "gelu_tanh"), names (optional): up, down
+class DenseFFN : public FeedForward {
+public:
+    DenseFFN(const PartSpec &s, DType dt, Device *d) : FeedForward(s, dt, d) {
+        hidden_ = s.get_int("hidden_size");
+        inter_ = s.get_int("intermediate_size");
+        if (hidden_ <= 0 || inter_ <= 0) config_error("dense: sizes must be positive");
+        std::string act = s.params.get("activation").is_string() ? s.params.get("activation").as_string() : "";
+        act_ = ops::activation_kind(act);
+        if (act_ < 0) config_error("dense: activation '" + act + "' is not one of relu2, relu, gelu_tanh");
+        const Json &nm = s.params.get("names");
+        n_up_ = nm.is_object() && nm.get("up").is_string() ? nm.get("up").as_string() : "up_proj.weight";
+        n_down_ = nm.is_object() && nm.get("down").is_string() ? nm.get("down").as_string() : "down_proj.weight";
+    }
+
+    void tensors(const std::string &prefix, TensorList &out) const override {
+        out.emplace_back(name(prefix, n_up_), TensorSpec{{inter_, hidden_}, MATRIX, false});
+        out.emplace_back(name(prefix, n_down_), TensorSpec{{hidden_, inter_}, MATRIX, false});
+    }
+
+    void load(const std::string &prefix, TensorMap &t) override {
+        w_up_ = take(t, name(prefix, n_up_));
+        w_down_ = take(t, name(prefix, n_down_));
+    }
+
+    size_t weight_bytes() const override { return w_up_.bytes() + w_down_.bytes(); }
+
+    Stack forward(StepContext &ctx, const void *h) override {
+        Device &d = *ctx.dev;
+        long long n = ctx.n_rows;
+        Stack z = ops::linear(d, h, ctx.dtype, n, hidden_, w_up_);
+        Buf act = ops::activation(d, z, inter_, act_, ctx.dtype);
+        z = Stack();
+        return ops::linear(d, act.ptr, ctx.dtype, n, inter_, w_down_);
+    }
+
+private:
+    long long hidden_, inter_;
+    int act_;
+    std::string n_up_, n_down_;
+    DevTensor w_up_, w_down_;
+};
+
 }  // namespace
 
 void register_builtin_feed_forwards() {
+    register_part("feed_forward", "dense", [](const PartSpec &s, DType dt, Device *d) {
+        return std::unique_ptr<Part>(new DenseFFN(s, dt, d));
+    });
     register_part("feed_forward", "polynorm", [](const PartSpec &s, DType dt, Device *d) {
         return std::unique_ptr<Part>(new PolyNormFFN(s, dt, d));
     });

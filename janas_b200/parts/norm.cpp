@@ -104,9 +104,76 @@ private:
     DevTensor w_, b_, alpha_;
 };
 
+// Layer norm with weight and bias: (x - mean) / sqrt(var + eps) * w + b, the variance
+// being the mean of the squared deviations.  Weight and bias are kept in float32.
+// params: size, eps, names (optional): weight, bias: the tensors' leaves below the
+// part's prefix ("" for the prefix itself); bias null: no bias
+class LayerNorm : public Norm {
+public:
+    LayerNorm(const PartSpec &s, DType dt, Device *d) : Norm(s, dt, d) {
+        size_ = s.get_int("size");
+        eps_ = (float)s.get_double("eps");
+        if (size_ <= 0) config_error("layernorm: size must be positive");
+        const Json &nm = s.params.get("names");
+        w_name_ = nm.is_object() && nm.get("weight").is_string() ? nm.get("weight").as_string() : "weight";
+        has_bias_ = !(nm.is_object() && nm.has("bias") && nm.get("bias").is_null());
+        b_name_ = nm.is_object() && nm.get("bias").is_string() ? nm.get("bias").as_string() : "bias";
+    }
+
+    void tensors(const std::string &prefix, TensorList &out) const override {
+        out.emplace_back(name(prefix, w_name_), TensorSpec{{size_}, PARAM, false, 1.0f, 0.1f});
+        if (has_bias_) out.emplace_back(name(prefix, b_name_), TensorSpec{{size_}, PARAM, false, 0.0f, 0.02f});
+    }
+
+    void load(const std::string &prefix, TensorMap &t) override {
+        w_ = take(t, name(prefix, w_name_));
+        if (has_bias_) b_ = take(t, name(prefix, b_name_));
+    }
+
+    size_t weight_bytes() const override { return w_.bytes() + b_.bytes(); }
+
+    ops::LnParams params() const {
+        ops::LnParams p;
+        p.w = (const float *)w_.ptr;
+        p.b = has_bias_ ? (const float *)b_.ptr : nullptr;
+        p.eps = eps_;
+        return p;
+    }
+
+    Buf apply(StepContext &ctx, float *x, long long n, DType out_dt, const Stack *delta, const int32_t *rows,
+              long long n_out) override {
+        return ops::layernorm(*ctx.dev, x, n, size_, params(), out_dt, delta, nullptr, 1.0f, rows, n_out);
+    }
+
+    Buf apply_after_add(StepContext &ctx, float *x, long long n, DType out_dt, const Stack &a, const Stack *b,
+                        float mult) override {
+        return ops::layernorm(*ctx.dev, x, n, size_, params(), out_dt, &a, b, mult, nullptr, 0);
+    }
+
+    long long size() const override { return size_; }
+
+    Json info() const override {
+        Json o = Json::object();
+        o.set("size", size_);
+        o.set("eps", (double)eps_);
+        o.set("bias", has_bias_);
+        return o;
+    }
+
+private:
+    long long size_;
+    float eps_;
+    bool has_bias_ = true;
+    std::string w_name_, b_name_;
+    DevTensor w_, b_;
+};
+
 }  // namespace
 
 void register_builtin_norms() {
+    register_part("norm", "layernorm", [](const PartSpec &s, DType dt, Device *d) {
+        return std::unique_ptr<Part>(new LayerNorm(s, dt, d));
+    });
     register_part("norm", "dynamic_tanh", [](const PartSpec &s, DType dt, Device *d) {
         return std::unique_ptr<Part>(new DynamicTanh(s, dt, d));
     });

@@ -129,6 +129,14 @@ public:
     // returned.  The result is [n or n_out, size] in out_dt.
     virtual Buf apply(StepContext &ctx, float *x, long long n, DType out_dt, const Stack *delta,
                       const int32_t *rows, long long n_out) = 0;
+    // x += mult * (sum a + sum b) in place (b may be null), then the norm of every row.
+    // A norm whose kernel takes the add in front of it does both in one pass; the rest
+    // run the add as a launch of its own.
+    virtual Buf apply_after_add(StepContext &ctx, float *x, long long n, DType out_dt, const Stack &a,
+                                const Stack *b, float mult) {
+        ops::add_scaled_(*ctx.dev, x, n, size(), a, b, mult);
+        return apply(ctx, x, n, out_dt, nullptr, nullptr, 0);
+    }
     virtual long long size() const = 0;
     // A norm that works value by value as tanh(alpha x) w + b says so here and gives
     // its parameters, so that a block can take it into the kernel that ends a

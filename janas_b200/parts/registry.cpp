@@ -119,7 +119,8 @@ std::unique_ptr<Block> build_block(const LayerSpec &ls, DType dt, Device *dev) {
     p.mixer_norm = build_norm(ls.mixer_norm, dt, dev);
     if (!ls.feed_forward.kind.empty()) {
         p.feed_forward = build_feed_forward(ls.feed_forward, dt, dev);
-        p.ffn_norm = build_norm(ls.ffn_norm, dt, dev);
+        // an arrangement whose sublayers share one norm names no ffn_norm
+        if (!ls.ffn_norm.kind.empty()) p.ffn_norm = build_norm(ls.ffn_norm, dt, dev);
     }
     if (!ls.post_mixer_norm.kind.empty()) p.post_mixer_norm = build_norm(ls.post_mixer_norm, dt, dev);
     if (!ls.post_ffn_norm.kind.empty() && p.feed_forward) p.post_ffn_norm = build_norm(ls.post_ffn_norm, dt, dev);

@@ -7,6 +7,11 @@
 // the table of cos and sin is filled on the device from double-precision sincos of
 // the float angle (src/llm/jmath.c:163-200) when the cache's size is known.
 //
+// rope_pairs is the same table for the layout that rotates neighbours: the pair
+// (2i, 2i + 1) turns by theta(p, i) = (float)p * (float)(theta ^ (-2 i / rotary_dim)),
+// the power taken in double and rounded once.  A mixer's own kernel applies it
+// (csrc/latent.cu); rotary_dim may be shorter than what it is applied to.
+//
 // The rotation itself is applied by the attention kernel that also normalizes the
 // heads and appends K and V (csrc/rope.cu); this part owns the constants and the
 // table.  Only the whole head can be rotated (rotary_dim == head size); the
@@ -22,7 +27,7 @@ namespace {
 // params: rotary_dim, theta, max_positions
 class RopeNeox : public PositionEncoding {
 public:
-    RopeNeox(const PartSpec &s, DType dt, Device *d) : PositionEncoding(s, dt, d) {
+    RopeNeox(const PartSpec &s, DType dt, Device *d, bool pairs = false) : PositionEncoding(s, dt, d) {
         rotary_dim_ = (int)s.get_int("rotary_dim");
         theta_ = s.get_double("theta");
         max_positions_ = s.get_int("max_positions");
@@ -32,7 +37,8 @@ public:
         for (int i = 0; i < half; i++) {
             // the exponent in float arithmetic, the power in double, rounded once
             float expo = -2.0f * (float)i / (float)rotary_dim_;
-            inv_freq_[(size_t)i] = (float)std::pow((double)(float)theta_, (double)expo);
+            inv_freq_[(size_t)i] = pairs ? (float)std::pow(theta_, -2.0 * (double)i / (double)rotary_dim_)
+                                         : (float)std::pow((double)(float)theta_, (double)expo);
         }
     }
 
@@ -87,6 +93,9 @@ public:
 void register_builtin_positions() {
     register_part("position", "rope_neox", [](const PartSpec &s, DType dt, Device *d) {
         return std::unique_ptr<Part>(new RopeNeox(s, dt, d));
+    });
+    register_part("position", "rope_pairs", [](const PartSpec &s, DType dt, Device *d) {
+        return std::unique_ptr<Part>(new RopeNeox(s, dt, d, true));
     });
     register_part("position", "none", [](const PartSpec &s, DType dt, Device *d) {
         return std::unique_ptr<Part>(new NoPosition(s, dt, d));
