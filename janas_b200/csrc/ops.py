@@ -371,10 +371,12 @@ def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float,
 def qkv_bias_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], row_pos: torch.Tensor,
                     row_seq: torch.Tensor, block_table: torch.Tensor,
                     k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                    num_heads: int, head_dim: int, out_dtype: torch.dtype) -> torch.Tensor:
+                    num_heads: int, head_dim: int, out_dtype: torch.dtype,
+                    q_temp_coef: float = 0.0, q_temp_every: int = 0) -> torch.Tensor:
     """The fused [q | k | v] product's sums plus its bias: returns q [n, heads, hd] in
     out_dtype and writes K and V to the cache pages at the rows' positions; with no
-    caches the product holds q alone."""
+    caches the product holds q alone.  With q_temp_every > 0 the queries of a row at
+    position p are multiplied by 1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1)."""
     qkv = stack(qkv)
     _need(qkv, "qkv", torch.float32, (None, None, None))
     S, n, width = qkv.shape
@@ -382,11 +384,127 @@ def qkv_bias_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], row_pos: to
     nkv = k_cache.shape[1] if append else 0
     vd = v_cache.shape[3] if append else 0
     q = torch.empty((n, num_heads, head_dim), dtype=out_dtype, device=qkv.device)
-    _check(lib().jb_qkv_bias_append(_p(qkv), S, n * width, width, _p(bias), _p(row_pos), _p(row_seq),
-                                    _p(block_table), block_table.shape[1], _p(q), _p(k_cache),
-                                    _p(v_cache), _DT[out_dtype], n, num_heads, nkv, head_dim, vd,
-                                    1 if append else 0, _stream()), "qkv_bias_append")
+    _check(lib().jb_qkv_bias_append_temp(_p(qkv), S, n * width, width, _p(bias), _p(row_pos),
+                                         _p(row_seq), _p(block_table), block_table.shape[1], _p(q),
+                                         _p(k_cache), _p(v_cache), _DT[out_dtype], n, num_heads, nkv,
+                                         head_dim, vd, 1 if append else 0, float(q_temp_coef),
+                                         int(q_temp_every), _stream()), "qkv_bias_append")
     return q
+
+
+def layernorm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+              eps: float, out_dtype: torch.dtype, a: Optional[torch.Tensor] = None,
+              b: Optional[torch.Tensor] = None, mult: float = 1.0,
+              rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """Layer norm with weight and bias of the rows of x (float32 [n, dm]).  With ``a``
+    (and ``b``), stacks of partial sums [S, n, dm], x += mult * (sum a + sum b) happens
+    first, in place.  ``rows``: only those rows (no add then).  ``weight`` None: the add
+    alone, nothing is returned."""
+    _need(x, "x", torch.float32, (None, None))
+    n, dm = x.shape
+    sa = sb = None
+    if a is not None:
+        sa = stack(a)
+        _need(sa, "a", torch.float32, (None, n, dm))
+    if b is not None:
+        sb = stack(b)
+        _need(sb, "b", torch.float32, (None, n, dm))
+    n_out = n if rows is None else rows.numel()
+    out = None
+    if weight is not None:
+        _need(weight, "weight", torch.float32, (dm,))
+        out = torch.empty((n_out, dm), dtype=out_dtype, device=x.device)
+    _check(lib().jb_layernorm(_p(x), _p(sa), 0 if sa is None else sa.shape[0], n * dm, _p(sb),
+                              0 if sb is None else sb.shape[0], n * dm, float(mult), _p(rows),
+                              _p(weight), _p(bias), _p(out), _DT[out_dtype], n_out, dm, float(eps),
+                              _stream()), "layernorm")
+    return out
+
+
+ACTIVATIONS = {"relu2": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def activation(z: torch.Tensor, kind: str, out_dtype: torch.dtype, ff: Optional[int] = None) -> torch.Tensor:
+    """act(sum of the partial sums z [S, n, width]) over the first ff columns."""
+    z = stack(z)
+    _need(z, "z", torch.float32, (None, None, None))
+    S, n, width = z.shape
+    ff = width if ff is None else ff
+    out = torch.empty((n, ff), dtype=out_dtype, device=z.device)
+    _check(lib().jb_activation(_p(z), S, n * width, width, ACTIVATIONS[kind], _p(out), _DT[out_dtype],
+                               n, ff, _stream()), "activation")
+    return out
+
+
+def latent_down(P: torch.Tensor, q_rank: int, wq: Optional[torch.Tensor], kv_rank: int,
+                wkv: torch.Tensor, rot_dim: int, cos: Optional[torch.Tensor],
+                sin: Optional[torch.Tensor], row_pos: torch.Tensor, row_seq: torch.Tensor,
+                block_table: torch.Tensor, k_cache: torch.Tensor, eps: float) -> torch.Tensor:
+    """P: sums [S, n, >= q_rank + kv_rank + rot_dim], columns [query latent | latent |
+    shared key part].  Returns the RMS-normed query latent [n, q_rank] in the cache's
+    dtype and writes [RMS-normed latent | rotated key part] to the cache rows
+    (k_cache [pages, 1, PAGE, kv_rank + rot_dim]) at the rows' positions."""
+    P = stack(P)
+    _need(P, "P", torch.float32, (None, None, None))
+    S, n, ld = P.shape
+    _need(k_cache, "k_cache", _FLOATS, (None, 1, PAGE, kv_rank + rot_dim))
+    rot_half = 0 if cos is None else cos.shape[1]
+    cq = torch.empty((n, q_rank), dtype=k_cache.dtype, device=P.device)
+    _check(lib().jb_latent_down(_p(P), S, n * ld, ld, 0, q_rank, _p(wq), q_rank, kv_rank, _p(wkv),
+                                rot_dim, _p(cos), _p(sin), rot_half, _p(row_pos), _p(row_seq),
+                                _p(block_table), block_table.shape[1], _p(cq), _p(k_cache),
+                                _DT[k_cache.dtype], n, float(eps), _stream()), "latent_down")
+    return cq
+
+
+def latent_queries(Q: torch.Tensor, w_ukT: torch.Tensor, num_heads: int, D: int, R: int, C: int,
+                   cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], row_pos: torch.Tensor,
+                   dtype: torch.dtype) -> torch.Tensor:
+    """Q: the query product's sums [S, n, heads (D + R)]; w_ukT [heads C, D]: per head
+    the key matrix, transposed.  Returns the latent queries [n, heads, C + R]: per head
+    [Wuk_head^T q_plain | rotated q_rot]."""
+    Q = stack(Q)
+    _need(Q, "Q", torch.float32, (None, None, num_heads * (D + R)))
+    S, n, _ = Q.shape
+    rot_half = 0 if cos is None else cos.shape[1]
+    q_plain = torch.empty((num_heads, n, D), dtype=dtype, device=Q.device)
+    q_lat = torch.empty((n, num_heads, C + R), dtype=dtype, device=Q.device)
+    L = lib()
+    _check(L.jb_latent_q_split(_p(Q), S, Q.shape[1] * Q.shape[2], num_heads, D, R, C, _p(cos), _p(sin),
+                               rot_half, _p(row_pos), _p(q_plain), _p(q_lat), _DT[dtype], n, _stream()),
+           "latent_q_split")
+    A = torch.stack([stack(linear(q_plain[h], w_ukT[h * C:(h + 1) * C], force_simt=True))
+                     for h in range(num_heads)])
+    _check(L.jb_latent_q_join(_p(A.contiguous()), A.shape[1], num_heads, C, R, _p(q_lat), _DT[dtype], n,
+                              _stream()), "latent_q_join")
+    return q_lat
+
+
+def heads_gate(A: torch.Tensor, g: Optional[torch.Tensor], g_col0: int,
+               out_dtype: torch.dtype) -> torch.Tensor:
+    """A: per-head sums [heads, S, n, Dv]; g: a gate's sums [Sg, n, width] whose columns
+    g_col0.. are the gate (or None).  Returns [n, heads Dv] = concat(sum A) * sigmoid(sum g)."""
+    _need(A, "A", torch.float32, (None, None, None, None))
+    H, S, n, Dv = A.shape
+    sg = None
+    if g is not None:
+        sg = stack(g)
+        _need(sg, "g", torch.float32, (None, n, None))
+    out = torch.empty((n, H * Dv), dtype=out_dtype, device=A.device)
+    _check(lib().jb_heads_gate(_p(A), S, H, Dv, _p(sg), 0 if sg is None else sg.shape[0],
+                               0 if sg is None else n * sg.shape[2], 0 if sg is None else sg.shape[2],
+                               g_col0, _p(out), _DT[out_dtype], n, _stream()), "heads_gate")
+    return out
+
+
+def transpose_heads(w: torch.Tensor, num_heads: int) -> torch.Tensor:
+    """w [heads D, C] -> [heads C, D]: every head's block transposed."""
+    _need(w, "w", _FLOATS, (None, None))
+    D, C = w.shape[0] // num_heads, w.shape[1]
+    out = torch.empty((num_heads * C, D), dtype=w.dtype, device=w.device)
+    _check(lib().jb_transpose_heads(_p(w), _p(out), _DT[w.dtype], num_heads, D, C, _stream()),
+           "transpose_heads")
+    return out
 
 
 def attention_chunk() -> int:
@@ -429,8 +547,15 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               window: int, scale: float, max_chunks: int, blocks: Optional[torch.Tensor] = None,
               decode: bool = False, force_simt: bool = False,
               head_scale: Optional[torch.Tensor] = None,
-              sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+              sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
+              slopes: Optional[torch.Tensor] = None, value_dim: int = 0,
+              head_major: bool = False) -> torch.Tensor:
     """Causal GQA attention of every row over its sequence's cache pages.
+
+    ``softcap`` > 0: a score s becomes softcap * tanh(s / softcap); ``slopes`` (float32
+    [heads]): slopes[h] * (the row's position - the key's) is taken off the score, after
+    the cap.  ``value_dim`` > 0 with ``v_cache is None``: the values are the first
+    value_dim entries of the keys' rows.  ``head_major``: the result is [heads, n, vd].
 
     q: [n, heads, hd]; caches [pages, kv_heads, PAGE, hd] of q's dtype.  Row r
     is at position row_pos[r] of sequence row_seq[r], whose pages are
@@ -452,8 +577,16 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     n, nh, hd = q.shape
     _need(k_cache, "k_cache", q.dtype, (None, None, PAGE, hd))
     nkv = k_cache.shape[1]
-    _need(v_cache, "v_cache", q.dtype, (k_cache.shape[0], nkv, PAGE, None))
-    vd = v_cache.shape[3]
+    v_ld = 0
+    if v_cache is None:
+        if not 0 < value_dim <= hd:
+            raise KernelError("attention: values inside the keys' rows need 0 < value_dim <= head size")
+        v_cache, vd, v_ld = k_cache, value_dim, hd
+    else:
+        _need(v_cache, "v_cache", q.dtype, (k_cache.shape[0], nkv, PAGE, None))
+        vd = v_cache.shape[3]
+    if slopes is not None:
+        _need(slopes, "slopes", torch.float32, (nh,))
     if head_scale is not None:
         _need(head_scale, "head_scale", torch.float32, (nh,))
     if sink is not None:
@@ -461,9 +594,10 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     _need(row_pos, "row_pos", torch.int32, (n,))
     _need(row_seq, "row_seq", torch.int32, (n,))
     _need(block_table, "block_table", torch.int32, (None, None))
-    out = torch.empty((n, nh, vd), dtype=q.dtype, device=q.device)
+    out = torch.empty((nh, n, vd) if head_major else (n, nh, vd), dtype=q.dtype, device=q.device)
     L = lib()
     tc = (not force_simt and vd == hd and q.dtype == torch.bfloat16
+          and softcap == 0.0 and slopes is None and v_ld == 0 and not head_major
           and (decode or blocks is not None) and bool(L.jb_attn_tc_ok(nh, nkv, hd))
           and (decode or head_scale is None or bool((head_scale > 0).all())))
     if tc and not decode:
@@ -502,11 +636,12 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                              cnt, nh, hd, window, parts, per_cta, _p(sink),
                                              _stream()), "attention merge")
         else:
-            _check(L.jb_attention_sink(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
-                                       _p(row_seq), _p(block_table), block_table.shape[1],
-                                       _p(scratch), _p(out), row0, cnt, nh, nkv, hd, vd, window,
-                                       float(scale), _p(head_scale), _p(sink), max_chunks,
-                                       _stream()), "attention", kernels=2)
+            _check(L.jb_attention_ext(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
+                                      _p(row_seq), _p(block_table), block_table.shape[1],
+                                      _p(scratch), _p(out), row0, cnt, nh, nkv, hd, vd, window,
+                                      float(scale), _p(head_scale), _p(sink), max_chunks, v_ld,
+                                      float(softcap), _p(slopes), n if head_major else 0,
+                                      _stream()), "attention", kernels=2)
     return out
 
 

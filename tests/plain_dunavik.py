@@ -79,6 +79,53 @@ def softmax_rows(s: torch.Tensor) -> torch.Tensor:
     return e / e.sum(dim=1, keepdim=True)
 
 
+def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, pos0: int = 0,
+                   window: int = 0, cap: float = 0.0, slope_exponent: Optional[float] = None) -> torch.Tensor:
+    """q [T, H, D] at positions pos0 .. pos0 + T - 1; k [S, G, D], v [S, G, Dv] at positions
+    0 .. S - 1.  Returns [T, H, Dv]."""
+    T, H, _ = q.shape
+    S, G, Dv = v.shape
+    i = torch.arange(T).unsqueeze(1) + pos0
+    j = torch.arange(S).unsqueeze(0)
+    out = torch.zeros(T, H, Dv)
+    for a in range(H):
+        g = a // (H // G)
+        s = (q[:, a] @ k[:, g].T) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        if slope_exponent is not None:
+            s = s - 2.0 ** (-slope_exponent * (a + 1) / H) * (i - j).to(torch.float32)
+        s = s.masked_fill(j > i, -math.inf)
+        if window:
+            s = s.masked_fill(i - j >= window, -math.inf)
+        out[:, a] = softmax_rows(s) @ v[:, g]
+    return out
+
+
+def latent_core(q_plain: torch.Tensor, q_rot: torch.Tensor, c: torch.Tensor, kr: torch.Tensor,
+                w_uk: torch.Tensor, w_uv: torch.Tensor, scale: float, pos0: int = 0) -> torch.Tensor:
+    """q_plain [T, H, D], q_rot [T, H, R] (rotated already) at positions pos0 ..; c [S, C] latents
+    and kr [S, R] rotated shared key parts at positions 0 .. S - 1; w_uk [H D, C], w_uv [H Dv, C].
+    Keys and values per head are formed here, plainly.  Returns [T, H, Dv]."""
+    T, H, D = q_plain.shape
+    S = c.shape[0]
+    Dv = w_uv.shape[0] // H
+    k_plain = (c @ w_uk.T).reshape(S, H, D)
+    v = (c @ w_uv.T).reshape(S, H, Dv)
+    i = torch.arange(T).unsqueeze(1) + pos0
+    j = torch.arange(S).unsqueeze(0)
+    out = torch.zeros(T, H, Dv)
+    for a in range(H):
+        s = (q_plain[:, a] @ k_plain[:, a].T + q_rot[:, a] @ kr.T) * scale
+        s = s.masked_fill(j > i, -math.inf)
+        out[:, a] = softmax_rows(s) @ v[:, a]
+    return out
+
+
+def query_temperature(pos: torch.Tensor, coef: float, every: int) -> torch.Tensor:
+    return 1.0 + coef * torch.log(torch.floor((pos + 1).to(torch.float32) / every) + 1.0)
+
+
 def latent_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mx: dict, eps: float,
                      rounding: Optional[str] = None) -> torch.Tensor:
     """h [T, W] at positions 0 .. T-1 -> the mixer's output [T, W]."""
@@ -90,49 +137,26 @@ def latent_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mx: di
     z = h @ w[p + "dkv"].T
     c = _round(rms(z[:, :C], w[p + "dkv.norm"], eps), rounding)
     kr = _round(rotate_pairs(z[:, C:], pos, mx["rot"]["base"], mx["rot"]["dims"]), rounding)
-    q_plain = q[:, :, :D]
-    q_rot = rotate_pairs(q[:, :, D:], pos, mx["rot"]["base"], mx["rot"]["dims"])
-    k_plain = (c @ w[p + "uk"].T).reshape(T, H, D)
-    v = (c @ w[p + "uv"].T).reshape(T, H, Dv)
-    i = torch.arange(T).unsqueeze(1)
-    j = torch.arange(T).unsqueeze(0)
-    out = torch.zeros(T, H, Dv)
-    for a in range(H):
-        s = (_round(q_plain[:, a], rounding) @ k_plain[:, a].T + _round(q_rot[:, a], rounding) @ kr.T) * mx["scale"]
-        s = s.masked_fill(j > i, -math.inf)
-        out[:, a] = softmax_rows(s) @ v[:, a]
+    q_plain = _round(q[:, :, :D], rounding)
+    q_rot = _round(rotate_pairs(q[:, :, D:], pos, mx["rot"]["base"], mx["rot"]["dims"]), rounding)
+    out = latent_core(q_plain, q_rot, c, kr, w[p + "uk"], w[p + "uv"], mx["scale"])
     g = torch.sigmoid(h @ w[p + "g"].T)
-    return _round(_round(out.reshape(T, H * Dv), rounding) * g, rounding) @ w[p + "o"].T
+    return _round(out.reshape(T, H * Dv) * g, rounding) @ w[p + "o"].T
 
 
 def window_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mx: dict,
                      rounding: Optional[str] = None) -> torch.Tensor:
     T = h.shape[0]
     H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
-    pos = torch.arange(T)
     q = (h @ w[p + "q"].T).reshape(T, H, D)
     qt = mx.get("q_temp")
     if qt:
-        t = 1.0 + qt["coef"] * torch.log(torch.floor((pos + 1).to(torch.float32) / qt["every"]) + 1.0)
-        q = q * t.reshape(T, 1, 1)
+        q = q * query_temperature(torch.arange(T), qt["coef"], qt["every"]).reshape(T, 1, 1)
     q = _round(q, rounding)
     k = _round((h @ w[p + "k"].T).reshape(T, G, D), rounding)
     v = _round((h @ w[p + "v"].T).reshape(T, G, Dv), rounding)
-    i = torch.arange(T).unsqueeze(1)
-    j = torch.arange(T).unsqueeze(0)
-    out = torch.zeros(T, H, Dv)
-    cap = mx.get("softcap")
-    win = (mx.get("mask") or {}).get("size", 0)
-    for a in range(H):
-        g = a // (H // G)
-        s = (q[:, a] @ k[:, g].T) * mx["scale"]
-        if cap:
-            s = cap * torch.tanh(s / cap)
-        s = s - 2.0 ** (-8.0 * (a + 1) / H) * (i - j).to(torch.float32)
-        s = s.masked_fill(j > i, -math.inf)
-        if win:
-            s = s.masked_fill(i - j >= win, -math.inf)
-        out[:, a] = softmax_rows(s) @ v[:, g]
+    out = attention_core(q, k, v, mx["scale"], 0, (mx.get("mask") or {}).get("size", 0),
+                         mx.get("softcap") or 0.0, 8.0)
     return _round(out.reshape(T, H * Dv), rounding) @ w[p + "o"].T
 
 
