@@ -8,6 +8,7 @@
     python bench.py --only decode|prefill|timeline ...   (one part, for profiling)
     python bench.py --only generate [--model 8b] ...      (unequal prompts, then 256 tokens each)
     python bench.py --only zuzelorn [--layers 8]           (the Zuzelorn design beside Qwen3 at equal sizes)
+    python bench.py --only dunavik [--design-size 4b]      (the Dunavik design beside Zuzelorn at equal sizes)
 
 The default run has the layer sizes of Qwen3-4B (36 layers, hidden 2560, 32
 heads, 8 KV heads, head size 128, feed-forward 9728, vocabulary 151936, tied
@@ -396,6 +397,55 @@ def zuzelorn_cfg(size, n_layers, vocab, max_positions, share=0):
             "max_positions": max_positions, "norm": {"eps": 1e-5}, "vocab": vocab, "width": dm}
 
 
+# the latent mixer's sizes beside each of the layer sizes above: latent, query latent, plain and
+# rotated key values per head (the values per head are the size's head size)
+LATENT_SIZES = {"1b": (256, 512, 64, 64), "4b": (384, 768, 64, 64), "8b": (448, 1024, 128, 64),
+                "4b-heads64": (384, 768, 64, 32)}
+
+
+def dunavik_cfg(size, n_layers, vocab, mixers="mixed", window=1024):
+    """A Dunavik config.json of the given layer sizes.  mixers: "attention" (every layer the
+    windowed, capped, sloped attention), "latent" (every layer the latent attention) or "mixed"
+    (every fourth layer latent, the first one first)."""
+    dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
+    C, Cq, D, R = LATENT_SIZES[size]
+    layers = []
+    for i in range(n_layers):
+        if mixers == "latent" or (mixers == "mixed" and i % 4 == 0):
+            m = {"dim": D, "heads": nh, "kv_rank": C, "q_rank": Cq, "rot": {"base": 10000.0, "dims": R},
+                 "rot_dim": R, "scale": (D + R) ** -0.5, "vdim": hd}
+            layers.append({"type": "latent_attention", "mixer": m, "mlp": {"ff": ff, "kind": "dense"}})
+        else:
+            m = {"dim": hd, "heads": nh, "kv_heads": nkv, "mask": {"size": window},
+                 "q_temp": {"coef": 0.1, "every": 512}, "scale": hd ** -0.5, "softcap": 30.0, "vdim": hd}
+            layers.append({"type": "attention", "mixer": m, "mlp": {"ff": ff, "kind": "dense"}})
+    return {"architecture": "Dunavik", "layers": layers, "loop": {"start": 0, "stop": 0, "times": 1},
+            "norm": {"eps": 1e-5}, "residual_mult": 0.7, "vocab": vocab, "width": dm}
+
+
+def dunavik_flops(cfg, tokens, window):
+    """Multiply-adds times two of one prompt of a Dunavik model: every product of every layer,
+    the attention over the keys a row sees (all before it, or the window), the head for one row."""
+    dm, total = cfg["width"], 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        H, Dv = m["heads"], m["vdim"]
+        if layer["type"] == "latent_attention":
+            C, Cq, D, R = m["kv_rank"], m["q_rank"], m["dim"], m["rot_dim"]
+            mats = dm * (Cq + C + R + H * Dv) + Cq * H * (D + R) + H * D * C + H * Dv * C + H * Dv * dm
+            pairs = tokens * (tokens + 1) / 2
+            attn = 2 * H * (2 * C + R) * pairs
+        else:
+            G, D = m["kv_heads"], m["dim"]
+            mats = dm * (H * D + G * D + G * Dv) + H * Dv * dm
+            w = m.get("mask", {}).get("size", 0) or tokens
+            pairs = sum(min(i + 1, w) for i in range(tokens))
+            attn = 2 * H * (D + Dv) * pairs
+        mats += 2 * dm * layer["mlp"]["ff"] if layer["mlp"] else 0
+        total += 2 * mats * tokens + attn
+    return total + 2 * dm * cfg["vocab"]
+
+
 def qwen3_cfg(size, n_layers, vocab, max_positions):
     dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
     return dict(QWEN3_4B, num_hidden_layers=n_layers, hidden_size=dm, num_attention_heads=nh,
@@ -462,12 +512,19 @@ def design_compare(args):
         if args.share:
             designs.append((f"zuzelorn-share{args.share}",
                             zuzelorn_cfg(size, n_layers, vocab, max_positions, args.share)))
+        if args.only == "dunavik":
+            # beside the design's closest relative: attention without a rotation, a feed-forward
+            # of two matrices
+            designs = [("zuzelorn", zuzelorn_cfg(size, n_layers, vocab, max_positions))]
+            designs += [(f"dunavik-{mx}", dunavik_cfg(size, n_layers, vocab, mx, args.window))
+                        for mx in args.mixers.split(",")]
         for design, cfg in designs:
             rng = np.random.default_rng(0)
             eng = Engine.open_random(cfg, seed=0, dtype=args.dtype, max_tokens=max(room * batch, T + 64),
                                      max_seqs=batch, n_ctx=max_positions)
             pre_ms = prefill_timed(eng, rng, T)
-            flops = design_flops(design.split("-")[0], size, n_layers, T, vocab)
+            flops = (dunavik_flops(cfg, T, args.window) if design.startswith("dunavik")
+                     else design_flops(design.split("-")[0], size, n_layers, T, vocab))
 
             def one_prefill():
                 s = eng.new_sequence()
@@ -531,12 +588,15 @@ def main():
                     help="skip decoding at batch 1 and 64 and the 32-bit points")
     ap.add_argument("--all-configs", action="store_true",
                     help="also the 8B workload (unequal prompts, 256 steps) and the 32B points")
+    ap.add_argument("--mixers", default="mixed,attention,latent",
+                    help="--only dunavik: which layer mixes to run (mixed, attention, latent), with commas")
+    ap.add_argument("--window", type=int, default=1024, help="--only dunavik: the attention layers' window")
     ap.add_argument("--design-size", default="", choices=[""] + sorted(DESIGN_SIZES),
                     help="--only zuzelorn: one of the layer sizes (default: 1b, 4b and 8b)")
     ap.add_argument("--share", type=int, default=0,
                     help="--only zuzelorn: also a model whose layers share keys and values in groups of this many")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "prefill-timeline", "generate",
-                                                    "zuzelorn"],
+                                                    "zuzelorn", "dunavik"],
                     help="run one part only and print its time (for profiling; no JSON line "
                          "but for generate); prefill-timeline: each kernel's share of one prefill "
                          "step; timeline: when each kernel of one replayed decode "
@@ -544,7 +604,9 @@ def main():
                          "--context], all in one step, then 256 tokens each through the Python "
                          "entry point; zuzelorn: prefill and decoding of a Zuzelorn model beside a "
                          "Qwen3 model of equal layer sizes (--layers, default 8), with every "
-                         "kernel's time")
+                         "kernel's time; dunavik: the same for Dunavik models (--mixers: every fourth "
+                         "layer latent attention, all windowed attention, all latent attention) beside "
+                         "a Zuzelorn model of equal layer sizes")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -552,7 +614,7 @@ def main():
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
-    if args.only == "zuzelorn":
+    if args.only in ("zuzelorn", "dunavik"):
         args.warmup = max(args.warmup, 3)
         return design_compare(args)
     full_layers = MODELS[args.model]["num_hidden_layers"]

@@ -62,6 +62,41 @@ __device__ __forceinline__ uint32_t swz(int row, int j)
     return (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4));
 }
 
+// What some mixers do to a score before the softmax, in the kernels' own units (scores
+// times log2 e): a cap, s <- cap * tanh(s / cap), and then a head's slope times the
+// key's distance back taken off.  cap2 = cap * log2(e) (0: no cap); slopes: float [nh]
+// in natural units, or null.
+struct ScoreExt {
+    float cap2;
+    const float *slopes;
+    __host__ __device__ bool on() const { return cap2 > 0.0f || slopes != nullptr; }
+};
+
+__device__ __forceinline__ float fast_tanh(float x)
+{
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// v2: a score in log2 units; slope2: the head's slope times log2(e); back: positions
+// between the query and the key
+__device__ __forceinline__ float ext_score(float v2, float cap2, float inv_cap2, float slope2,
+                                           int back)
+{
+    if (cap2 > 0.0f)
+        v2 = cap2 * fast_tanh(v2 * inv_cap2);
+    return fmaf(-slope2, (float)back, v2);
+}
+
+static ScoreExt score_ext(float softcap, const float *slopes)
+{
+    ScoreExt x;
+    x.cap2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+    x.slopes = slopes;
+    return x;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(192)
 attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -71,7 +106,7 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q,
                     const int32_t *__restrict__ block_table, int bt_stride,
                     float *__restrict__ part, int nh, int nkv, int G, int window, float scale,
                     int max_chunks, int chunks_per_cta, int row0,
-                    const float *__restrict__ head_scale)
+                    const float *__restrict__ head_scale, const ScoreExt x)
 {
     using Cfg = AttnCfg<HD>;
     constexpr int NB = Cfg::NB;
@@ -225,6 +260,9 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q,
         // scores in units of log2(e); a head may have a factor of its own
         const float c2 = scale * 1.4426950408889634f *
                          (head_scale != nullptr && live ? head_scale[kvh * G + g] : 1.0f);
+        const bool ext = x.on();
+        const float inv_cap2 = x.cap2 > 0.0f ? 1.0f / x.cap2 : 0.0f;
+        const float slope2 = x.slopes != nullptr && live ? x.slopes[kvh * G + g] * 1.4426950408889634f : 0.0f;
         bool ok = true;
         for (int it = 0; it < n_chunks; it++) {
             int c = c_first + it;
@@ -244,7 +282,8 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q,
                     for (int i = 0; i < 32; i++) {
                         int t = t0 + cb * 32 + i;
                         if (live && t <= pos && t >= lo)
-                            mx = fmaxf(mx, sc[i] * c2);
+                            mx = fmaxf(mx, ext ? ext_score(sc[i] * c2, x.cap2, inv_cap2, slope2, pos - t)
+                                               : sc[i] * c2);
                     }
                 }
                 m_new = mx;
@@ -257,9 +296,13 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         int t = t0 + cb * 32 + i;
-                        float p0 = (live && t <= pos && t >= lo) ? exp2f(sc[i] * c2 - m_new) : 0.0f;
-                        float p1 = (live && t + 1 <= pos && t + 1 >= lo)
-                                       ? exp2f(sc[i + 1] * c2 - m_new) : 0.0f;
+                        float s0 = sc[i] * c2, s1 = sc[i + 1] * c2;
+                        if (ext) {
+                            s0 = ext_score(s0, x.cap2, inv_cap2, slope2, pos - t);
+                            s1 = ext_score(s1, x.cap2, inv_cap2, slope2, pos - t - 1);
+                        }
+                        float p0 = (live && t <= pos && t >= lo) ? exp2f(s0 - m_new) : 0.0f;
+                        float p1 = (live && t + 1 <= pos && t + 1 >= lo) ? exp2f(s1 - m_new) : 0.0f;
                         l_chunk += p0 + p1;
                         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                         packed[i / 2] = *reinterpret_cast<uint32_t *>(&pk);
@@ -360,7 +403,7 @@ template <int HD> struct PrefillCfg {
     static constexpr int TMEM_COLS = 512;
 };
 
-template <int HD>
+template <int HD, bool EXT>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_k,
@@ -368,7 +411,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                        const int32_t *__restrict__ block_table, int bt_stride,
                        bf16 *__restrict__ out, int nh, int nkv, int G, int R, int window,
                        float scale, const float *__restrict__ head_scale,
-                       const float *__restrict__ sink)
+                       const float *__restrict__ sink, const ScoreExt x)
 {
     using Cfg = PrefillCfg<HD>;
     constexpr int NB = Cfg::NB;
@@ -569,6 +612,11 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         // the maximum below is taken before the factor is applied)
         const float c2 = scale * 1.4426950408889634f *
                          (head_scale != nullptr && live ? head_scale[kvh * G + g] : 1.0f);
+        // with a cap or slopes the scores are transformed in place and c2 is in them already
+        const float c2x = EXT ? 1.0f : c2;
+        const float inv_cap2 = EXT && x.cap2 > 0.0f ? 1.0f / x.cap2 : 0.0f;
+        const float slope2 = EXT && x.slopes != nullptr && live
+                                 ? x.slopes[kvh * G + g] * 1.4426950408889634f : 0.0f;
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (int it = 0; it < n_chunks && tile_live; it++) {
@@ -591,7 +639,22 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 // and scaled once; the scale itself goes into the exponent's FMA.
                 bool inside = t0 + AT_KEYS - 1 <= pos_first && t0 >= lo_last;
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                if (inside && live) {
+                if constexpr (EXT) {
+                    // every score goes through the cap and loses its head's slope times the
+                    // key's distance back: in log2 units, in place of the raw score
+#pragma unroll
+                    for (int i = 0; i < AT_KEYS; i += 4)
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            int key = t0 + i + e;
+                            float v = -INFINITY;
+                            if (live && key <= pos && key >= lo)
+                                v = ext_score(__uint_as_float(raw[i + e]) * c2, x.cap2, inv_cap2, slope2,
+                                              pos - key);
+                            raw[i + e] = __float_as_uint(v);
+                            m4[e] = fmaxf(m4[e], v);
+                        }
+                } else if (inside && live) {
 #pragma unroll
                     for (int i = 0; i < AT_KEYS; i += 4)
 #pragma unroll
@@ -609,7 +672,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                             m4[e] = fmaxf(m4[e], v);
                         }
                 }
-                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * c2;
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * c2x;
             }
             // move the row's reference only when the maximum has run far ahead of it
             bool move = mx > m_ref + PF_LAZY || (m_ref == -INFINITY && mx > -INFINITY);
@@ -628,8 +691,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             for (int i = 0; i < AT_KEYS / 2; i += 4) {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * (i + e)]), c2, -m_use));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * (i + e) + 1]), c2, -m_use));
+                    float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * (i + e)]), c2x, -m_use));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * (i + e) + 1]), c2x, -m_use));
                     l4[e] += p0 + p1;
                     __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                     raw[i + e] = *reinterpret_cast<uint32_t *>(&pk);
@@ -755,6 +818,8 @@ struct DecodeQkv {
     const float *bias;           // the product's bias over its columns, or nullptr
     const float *head_scale;     // a factor per head on the scores, or nullptr (also without qkv)
     long long ld;                // floats from one row of qkv to the next; 0: (nh + 2 nkv) HD
+    float cap2;                  // ScoreExt's fields: a cap on the scores (0: none) ...
+    const float *slopes;         // ... and a slope per head on the distance back, or nullptr
 };
 
 __device__ __forceinline__ float4 load_w4(const void *w, int w_f32, int at)
@@ -1071,6 +1136,12 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int g = 0; g < GP; g++)
             c2[g] = scale * 1.4426950408889634f *
                     (f.head_scale != nullptr && g < G ? f.head_scale[kvh * G + g] : 1.0f);
+        const bool ext = f.cap2 > 0.0f || f.slopes != nullptr;
+        const float inv_cap2 = f.cap2 > 0.0f ? 1.0f / f.cap2 : 0.0f;
+        float slope2[GP];
+#pragma unroll
+        for (int g = 0; g < GP; g++)
+            slope2[g] = f.slopes != nullptr && g < G ? f.slopes[kvh * G + g] * 1.4426950408889634f : 0.0f;
         bool ok = true;
         // running over this CTA's chunks: maximum, sum (every thread keeps all heads')
         // and this thread's value of O for every head
@@ -1110,6 +1181,8 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
             for (int g = 0; g < GP; g++) {
                 float v = (ok && visible && g < G) ? sc[g] * c2[g] : -INFINITY;
+                if (ext && v != -INFINITY)
+                    v = ext_score(v, f.cap2, inv_cap2, slope2[g], q_pos - t);
                 sc[g] = v;
                 m[g] = warp_max(v);
             }
@@ -1238,7 +1311,8 @@ static int launch_attn_rows(const void *q, const void *k_cache, const void *v_ca
                             long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
                             const int32_t *block_table, int bt_stride, float *part, int n, int nh,
                             int nkv, int window, float scale, int max_chunks, int chunks_per_cta,
-                            int row0, int n_rows, const float *head_scale, cudaStream_t st)
+                            int row0, int n_rows, const float *head_scale, ScoreExt x,
+                            cudaStream_t st)
 {
     using Cfg = AttnCfg<HD>;
     int G = nh / nkv;
@@ -1256,7 +1330,7 @@ static int launch_attn_rows(const void *q, const void *k_cache, const void *v_ca
         return JB_OK;
     launch(kern, dim3(gx, nkv), 192, Cfg::SMEM_BYTES, st, mq, mk, mv, row_pos, row_seq,
            block_table, bt_stride, part, nh, nkv, G, window, scale, max_chunks, chunks_per_cta,
-           row0, head_scale);
+           row0, head_scale, x);
     return launch_status();
 }
 
@@ -1302,8 +1376,24 @@ extern "C" int jb_attn_tc_prefill_sink(const void *q, const void *k_cache, const
                                        int nh, int nkv, int hd, int window, float scale,
                                        const float *head_scale, const float *sink, cudaStream_t st)
 {
-    if (!jb_attn_tc_ok(nh, nkv, hd) || n <= 0)
+    return jb_attn_tc_prefill_ext(q, k_cache, v_cache, n_pages, qblk, n_blocks, block_table,
+                                  bt_stride, out, n, nh, nkv, hd, window, scale, head_scale, sink,
+                                  0.0f, nullptr, st);
+}
+
+// The same with a cap on the scores (softcap > 0: s <- softcap * tanh(s / softcap), the
+// hardware's approximate tanh) and a slope per head (slopes, float [nh], or null):
+// slopes[h] * (the query's position - the key's) is taken off the score, after the cap.
+extern "C" int jb_attn_tc_prefill_ext(const void *q, const void *k_cache, const void *v_cache,
+                                      long long n_pages, const int32_t *qblk, int n_blocks,
+                                      const int32_t *block_table, int bt_stride, void *out, int n,
+                                      int nh, int nkv, int hd, int window, float scale,
+                                      const float *head_scale, const float *sink, float softcap,
+                                      const float *slopes, cudaStream_t st)
+{
+    if (!jb_attn_tc_ok(nh, nkv, hd) || n <= 0 || softcap < 0.0f)
         return JB_EINVAL;
+    ScoreExt x = score_ext(softcap, slopes);
     int G = nh / nkv;
     int R = AT_ROWS / G;               // positions of one block; qblk's runs hold up to 2 R
     CUtensorMap mq, mk, mv;
@@ -1313,20 +1403,24 @@ extern "C" int jb_attn_tc_prefill_sink(const void *q, const void *k_cache, const
         return JB_EINVAL;
     if (n_blocks <= 0)
         return JB_OK;
-#define JB_PF(HDV)                                                                             \
+#define JB_PF(HDV, EXT)                                                                        \
     do {                                                                                       \
         static unsigned long long smem_allowed = 0;                                            \
-        if (!allow_dynamic_smem(attn_tc_prefill_kernel<HDV>, PrefillCfg<HDV>::SMEM_BYTES,      \
-                                smem_allowed))                                                 \
+        auto kern = attn_tc_prefill_kernel<HDV, EXT>;                                          \
+        if (!allow_dynamic_smem(kern, PrefillCfg<HDV>::SMEM_BYTES, smem_allowed))              \
             return JB_ELAUNCH;                                                                 \
-        launch(attn_tc_prefill_kernel<HDV>, dim3((unsigned)n_blocks * nkv), PF_THREADS,        \
+        launch(kern, dim3((unsigned)n_blocks * nkv), PF_THREADS,                               \
                PrefillCfg<HDV>::SMEM_BYTES, st, mq, mk, mv, qblk, block_table, bt_stride,      \
-               (bf16 *)out, nh, nkv, G, R, window, scale, head_scale, sink);                   \
+               (bf16 *)out, nh, nkv, G, R, window, scale, head_scale, sink, x);                \
     } while (0)
-    if (hd == 128)
-        JB_PF(128);
+    if (hd == 128 && x.on())
+        JB_PF(128, true);
+    else if (hd == 128)
+        JB_PF(128, false);
+    else if (x.on())
+        JB_PF(64, true);
     else
-        JB_PF(64);
+        JB_PF(64, false);
 #undef JB_PF
     return launch_status();
 }
@@ -1380,10 +1474,12 @@ static int attn_tc_decode(const void *q, const void *k_cache, const void *v_cach
     if (hd == 128)
         return launch_attn_rows<128>(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
                                      bt_stride, part, n, nh, nkv, window, scale, max_chunks,
-                                     chunks_per_cta, row0, n_rows, f.head_scale, st);
+                                     chunks_per_cta, row0, n_rows, f.head_scale,
+                                     ScoreExt{f.cap2, f.slopes}, st);
     return launch_attn_rows<64>(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
                                 bt_stride, part, n, nh, nkv, window, scale, max_chunks,
-                                chunks_per_cta, row0, n_rows, f.head_scale, st);
+                                chunks_per_cta, row0, n_rows, f.head_scale, ScoreExt{f.cap2, f.slopes},
+                                st);
 }
 
 extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void *v_cache,
@@ -1408,6 +1504,28 @@ extern "C" int jb_attn_tc_decode_scaled(const void *q, const void *k_cache, cons
 {
     DecodeQkv f = {};
     f.head_scale = head_scale;
+    return attn_tc_decode(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table, bt_stride,
+                          part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
+                          chunks_per_cta, f, st);
+}
+
+// The same with a cap on the scores and a slope per head on the key's distance back
+// (see jb_attn_tc_prefill_ext).
+extern "C" int jb_attn_tc_decode_ext(const void *q, const void *k_cache, const void *v_cache,
+                                     long long n_pages, const int32_t *row_pos,
+                                     const int32_t *row_seq, const int32_t *block_table,
+                                     int bt_stride, float *part, int n, int row0, int n_rows,
+                                     int nh, int nkv, int hd, int window, float scale,
+                                     const float *head_scale, float softcap, const float *slopes,
+                                     int max_chunks, int chunks_per_cta, cudaStream_t st)
+{
+    if (softcap < 0.0f)
+        return JB_EINVAL;
+    DecodeQkv f = {};
+    f.head_scale = head_scale;
+    ScoreExt x = score_ext(softcap, slopes);
+    f.cap2 = x.cap2;
+    f.slopes = x.slopes;
     return attn_tc_decode(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table, bt_stride,
                           part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
                           chunks_per_cta, f, st);
@@ -1464,7 +1582,7 @@ extern "C" int jb_attn_tc_decode_qkv_bias(const float *qkv, int S, long long spl
         return JB_EINVAL;
     DecodeQkv f = {qkv, S, split_stride, q_w, k_w, w_dt == JB_F32, eps, cs, sn,
                    append ? (bf16 *)k_cache : nullptr, append ? (bf16 *)v_cache : nullptr, bias,
-                   head_scale, ld};
+                   head_scale, ld, 0.0f, nullptr};
     return attn_tc_decode(nullptr, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
                           bt_stride, part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
                           chunks_per_cta, f, st);

@@ -240,7 +240,7 @@ template <int BN, int MT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                float *__restrict__ out, bf16 *__restrict__ out_act, int n, int m, int k,
-               int second_off, int kb_per_split)
+               int second_off, int kb_per_split, int heads)
 {
     using Cfg = TileCfg<BN, MT, EPI == EPI_SWIGLU_HALF>;
     constexpr int STAGES = Cfg::STAGES;
@@ -263,7 +263,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                                                                                 : TILE_M * MT);
     int n0 = blockIdx.x * BN;
     int total_kb = (k + BK - 1) / BK;
-    int kb0 = blockIdx.z * kb_per_split;
+    // Several products of one shape in one launch (heads > 1): head h has rows h n ..
+    // of the activations and rows h m .. of the weights, and blockIdx.z counts
+    // (head, part of k), so that out + blockIdx.z n m is [head][part][n][m].
+    int parts_z = gridDim.z / heads;
+    int head = blockIdx.z / parts_z;
+    int w_row0 = m0 + head * m, a_row0 = n0 + head * n;
+    int kb0 = (blockIdx.z - head * parts_z) * kb_per_split;
     int nkb = min(kb_per_split, total_kb - kb0);
 
     uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
@@ -298,12 +304,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // of 64 rows, the gate's and the up projection's, that make one tile
         auto load_w = [&](uint32_t dst, uint32_t bar, int kx) {
             if (EPI == EPI_SWIGLU_HALF) {
-                tma_load_2d(dst, &map_w, bar, kx, m0);
-                tma_load_2d(dst + W_TILE_BYTES / 2, &map_w, bar, kx, m0 + second_off);
+                tma_load_2d(dst, &map_w, bar, kx, w_row0);
+                tma_load_2d(dst + W_TILE_BYTES / 2, &map_w, bar, kx, w_row0 + second_off);
             } else {
 #pragma unroll
                 for (int t = 0; t < MT; t++)
-                    tma_load_2d(dst + t * W_TILE_BYTES, &map_w, bar, kx, m0 + t * second_off);
+                    tma_load_2d(dst + t * W_TILE_BYTES, &map_w, bar, kx, w_row0 + t * second_off);
             }
         };
         int pre = min(nkb, STAGES);
@@ -317,7 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         pdl_wait();
         for (int i = 0; i < pre; i++)
             tma_load_2d(smem_u32(smem + i * Cfg::STAGE_BYTES) + MT * W_TILE_BYTES, &map_a,
-                        full0 + 8 * i, (kb0 + i) * BK, n0);
+                        full0 + 8 * i, (kb0 + i) * BK, a_row0);
         for (int i = pre; i < nkb; i++) {
             int s = i % STAGES;
             uint32_t ph = (i / STAGES) & 1;
@@ -328,7 +334,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_expect_tx(bar, Cfg::STAGE_BYTES);
             int kx = (kb0 + i) * BK;
             load_w(dst, bar, kx);
-            tma_load_2d(dst + MT * W_TILE_BYTES, &map_a, bar, kx, n0);
+            tma_load_2d(dst + MT * W_TILE_BYTES, &map_a, bar, kx, a_row0);
             armed |= 1u << s;
             last_parity = (last_parity & ~(1u << s)) | (ph << s);
         }
@@ -445,12 +451,12 @@ static bool tensor_map(const void *ptr, int rows, int k, int box_rows, CUtensorM
 
 template <int BN, int MT, int EPI>
 static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, int n, int m, int k,
-                     int w_rows, int second_off, int splits, cudaStream_t st)
+                     int w_rows, int second_off, int splits, cudaStream_t st, int heads = 1)
 {
     using Cfg = TileCfg<BN, MT, EPI == EPI_SWIGLU_HALF>;
     CUtensorMap map_w, map_a;
     if (!tensor_map(W, w_rows, k, EPI == EPI_SWIGLU_HALF ? HALF_M : TILE_M, &map_w) ||
-        !tensor_map(A, n, k, BN, &map_a))
+        !tensor_map(A, n * heads, k, BN, &map_a))
         return JB_EINVAL;
     auto kern = gemm_tc_kernel<BN, MT, EPI>;
     static unsigned long long smem_allowed = 0;
@@ -462,11 +468,11 @@ static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, in
         return JB_EINVAL;   // a part without work
     int feats = EPI == EPI_PARTIAL ? m : second_off;
     int tile_feats = EPI == EPI_SWIGLU ? TILE_M : EPI == EPI_SWIGLU_HALF ? HALF_M : TILE_M * MT;
-    dim3 grid((n + BN - 1) / BN, (feats + tile_feats - 1) / tile_feats, splits);
+    dim3 grid((n + BN - 1) / BN, (feats + tile_feats - 1) / tile_feats, splits * heads);
     if (grid.y > 65535 || grid.z > 65535)
         return JB_EINVAL;
     launch(kern, grid, GEMM_THREADS, Cfg::SMEM_BYTES, st, map_w, map_a, out, out_act, n, m, k, second_off,
-           kbps);
+           kbps, heads);
     return launch_status();
 }
 
@@ -601,10 +607,20 @@ static int many_tokens_splits(int n, int m, int k)
 extern "C" int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m, int k, int splits,
                           cudaStream_t st)
 {
-    if (!jb_gemm_tc_ok(A, W, n, m, k) || splits < 1)
+    return jb_gemm_tc_heads(A, W, out, n, m, k, splits, 1, st);
+}
+
+// `heads` products of one shape in one launch: A [heads, n, k], W [heads, m, k], out
+// [heads, splits, n, m]; head h multiplies its own rows of A with its own rows of W.
+extern "C" int jb_gemm_tc_heads(const void *A, const void *W, float *out, int n, int m, int k,
+                                int splits, int heads, cudaStream_t st)
+{
+    if (!jb_gemm_tc_ok(A, W, n, m, k) || splits < 1 || heads < 1 || (long long)splits * heads > 65535 ||
+        (long long)heads * m > 0x7fffffffll || (long long)heads * n > 0x7fffffffll)
         return JB_EINVAL;
+    const int wr = heads * m;
     if (n > 128) {
-#define JB_MANY(B) launch_tc<B, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st)
+#define JB_MANY(B) launch_tc<B, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, wr, TILE_M, splits, st, heads)
         switch (many_tokens_tile(n, m, k, splits)) {
         case 128: return JB_MANY(128);
         case 160: return JB_MANY(160);
@@ -615,12 +631,12 @@ extern "C" int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m
 #undef JB_MANY
     }
     if (n <= 16)
-        return launch_tc<16, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
+        return launch_tc<16, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, wr, TILE_M, splits, st, heads);
     if (n <= 32)
-        return launch_tc<32, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
+        return launch_tc<32, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, wr, TILE_M, splits, st, heads);
     if (n <= 64)
-        return launch_tc<64, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
-    return launch_tc<128, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
+        return launch_tc<64, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, wr, TILE_M, splits, st, heads);
+    return launch_tc<128, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, wr, TILE_M, splits, st, heads);
 }
 
 // W: [2 ff, k], rows [0, ff) the gate and [ff, 2 ff) the up projection.

@@ -153,6 +153,17 @@ int jb_attn_tc_decode_qkv_bias(const float *qkv, int S, long long split_stride, 
                                float *part, int n, int row0, int n_rows, int nh, int nkv, int hd,
                                int window, float scale, const float *head_scale, long long ld,
                                int max_chunks, int chunks_per_cta, cudaStream_t st);
+int jb_attn_tc_prefill_ext(const void *q, const void *k_cache, const void *v_cache,
+                           long long n_pages, const int32_t *qblk, int n_blocks,
+                           const int32_t *block_table, int bt_stride, void *out, int n, int nh,
+                           int nkv, int hd, int window, float scale, const float *head_scale,
+                           const float *sink, float softcap, const float *slopes, cudaStream_t st);
+int jb_attn_tc_decode_ext(const void *q, const void *k_cache, const void *v_cache,
+                          long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
+                          const int32_t *block_table, int bt_stride, float *part, int n, int row0,
+                          int n_rows, int nh, int nkv, int hd, int window, float scale,
+                          const float *head_scale, float softcap, const float *slopes,
+                          int max_chunks, int chunks_per_cta, cudaStream_t st);
 int jb_attn_tc_error(void);
 long long jb_gemm_simt_scratch(int n, int m, int k);
 int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, float *out, int n, int m, int k,
@@ -161,6 +172,8 @@ int jb_gemm_tc_ok(const void *A, const void *W, int n, int m, int k);
 int jb_gemm_tc_splits(int n, int m, int k);
 int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m, int k, int splits,
                cudaStream_t st);
+int jb_gemm_tc_heads(const void *A, const void *W, float *out, int n, int m, int k, int splits,
+                     int heads, cudaStream_t st);
 int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, int n, int ff, int k,
                       cudaStream_t st);
 int jb_gemm_tc_error(void);

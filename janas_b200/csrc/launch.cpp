@@ -332,23 +332,24 @@ HeadStack linear_heads(Device &d, const void *a, DType a_dt, int H, long long n,
     out.m = w.shape[0] / H;
     int ni = as_int(n, "rows"), mi = as_int(out.m, "features"), ki = as_int(k, "width");
     size_t a_head = (size_t)n * (size_t)k * dtype_size(a_dt), w_head = (size_t)out.m * (size_t)k * dtype_size(w.dt);
-    bool tc = n > 0 && a_dt == BF16 && w.dt == BF16;
-    for (int h = 0; h < H && tc; h++)
-        tc = jb_gemm_tc_ok((const char *)a + h * a_head, (const char *)w.ptr + h * w_head, ni, mi, ki) != 0;
+    // the tensor-core kernel takes all heads in one launch: rows of one head follow the other's
+    bool tc = n > 0 && a_dt == BF16 && w.dt == BF16 && jb_gemm_tc_ok(a, w.ptr, ni, mi, ki) != 0 &&
+              (long long)H * out.m <= 0x7fffffffll && (long long)H * n <= 0x7fffffffll;
     out.S = tc ? jb_gemm_tc_splits(ni, mi, ki) : 1;
     size_t one = (size_t)out.S * (size_t)n * (size_t)out.m;
     out.buf = d.pool.get(std::max<size_t>((size_t)H * one * 4, 16));
     long long need = tc ? 0 : jb_gemm_simt_scratch(ni, mi, ki);
     Buf scratch;
     if (need > 0) scratch = d.pool.get((size_t)need * 4);
+    if (tc) {
+        check(jb_gemm_tc_heads(a, w.ptr, out.data(), ni, mi, ki, out.S, H, d.stream), "linear_heads (tcgen05)");
+        return out;
+    }
     for (int h = 0; h < H && n > 0; h++) {
         const char *ah = (const char *)a + h * a_head, *wh = (const char *)w.ptr + h * w_head;
         float *oh = out.data() + (size_t)h * one;
-        if (tc)
-            check(jb_gemm_tc(ah, wh, oh, ni, mi, ki, out.S, d.stream), "linear_heads (tcgen05)");
-        else
-            check(jb_gemm_simt(ah, a_dt, wh, w.dt, oh, ni, mi, ki, scratch.as<float>(), d.stream),
-                  "linear_heads", need > 0 ? 2 : 1);
+        check(jb_gemm_simt(ah, a_dt, wh, w.dt, oh, ni, mi, ki, scratch.as<float>(), d.stream),
+              "linear_heads", need > 0 ? 2 : 1);
     }
     return out;
 }
@@ -436,12 +437,12 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
     int vd = g.value_dim();
     Buf out = d.pool.get((size_t)n * (size_t)g.nh * (size_t)vd * dtype_size(c.dt));
     bool tc = !force_simt && vd == g.hd && c.dt == BF16 && (decode || blocks != nullptr) &&
-              g.softcap == 0.0f && !g.slopes && !c.v_ld && !head_major &&
+              !c.v_ld && !head_major &&
               attention_tc_ok(g.nh, g.nkv, g.hd) && (decode || !g.head_scale || g.head_scale_positive);
     if (tc && !decode) {
-        check(jb_attn_tc_prefill_sink(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
-                                      out.ptr, ni, g.nh, g.nkv, g.hd, g.window, g.scale, g.head_scale,
-                                      g.sink, d.stream), "attention (tcgen05, prefill)");
+        check(jb_attn_tc_prefill_ext(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
+                                     out.ptr, ni, g.nh, g.nkv, g.hd, g.window, g.scale, g.head_scale,
+                                     g.sink, g.softcap, g.slopes, d.stream), "attention (tcgen05, prefill)");
         return out;
     }
     int parts = max_chunks, per_cta = 1;
@@ -459,10 +460,10 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
     for (long long row0 = 0; row0 < n; row0 += rows_per_call) {
         int cnt = (int)std::min<long long>(rows_per_call, n - row0);
         if (tc) {
-            check(jb_attn_tc_decode_scaled(q, c.k, c.v, c.n_pages, row_pos, row_seq, c.block_table,
-                                           c.bt_stride, scratch.as<float>(), ni, (int)row0, cnt, g.nh, g.nkv,
-                                           g.hd, g.window, g.scale, g.head_scale, max_chunks, per_cta,
-                                           d.stream), "attention (tcgen05, decode)");
+            check(jb_attn_tc_decode_ext(q, c.k, c.v, c.n_pages, row_pos, row_seq, c.block_table,
+                                        c.bt_stride, scratch.as<float>(), ni, (int)row0, cnt, g.nh, g.nkv,
+                                        g.hd, g.window, g.scale, g.head_scale, g.softcap, g.slopes,
+                                        max_chunks, per_cta, d.stream), "attention (tcgen05, decode)");
             check(jb_attention_merge_sink(scratch.as<float>(), row_pos, out.ptr, c.dt, (int)row0, cnt, g.nh,
                                           g.hd, g.window, parts, per_cta, g.sink, d.stream), "attention merge");
         } else {

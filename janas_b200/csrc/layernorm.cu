@@ -59,6 +59,72 @@ layernorm_kernel(float *__restrict__ x, const float *__restrict__ a, int Sa, siz
         o[i] = from_f<TO>(fmaf((row[i] - mean) * inv, w[i], bias != nullptr ? bias[i] : 0.0f));
 }
 
+// The same for few rows of the bfloat16 path: a cluster of C CTAs per row, each with a
+// slice of `cols` columns, so that the partial sums a decode step's products leave (many
+// per value) are fetched by many threads at once.  The two sums cross the cluster through
+// shared memory: every CTA writes its part into every CTA's array and adds the parts in
+// rank order.
+template <typename TO, int C>
+__global__ void __launch_bounds__(256)
+layernorm_cluster_kernel(float *__restrict__ x, const float *__restrict__ a, int Sa, size_t a_stride,
+                         const float *__restrict__ b, int Sb, size_t b_stride, float mult,
+                         const int32_t *__restrict__ row_idx, const float *__restrict__ w,
+                         const float *__restrict__ bias, TO *__restrict__ out, int dm, int cols,
+                         float eps)
+{
+    extern __shared__ float row[];          // this CTA's slice
+    __shared__ float red[32];
+    __shared__ float part_sum[C], part_sq[C];
+    pdl_trigger();
+    uint32_t rank = cluster_rank();
+    int r = blockIdx.x / C;
+    int c0 = (int)rank * cols, c1 = min(dm, c0 + cols);
+    pdl_wait();
+    size_t src = row_idx != nullptr ? (size_t)row_idx[r] : (size_t)r;
+    float *xr = x + src * dm;
+    float sum = 0.0f;
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
+        float v = xr[i];
+        if (a != nullptr) {
+            float d = add_partials(0.0f, a + src * dm + i, Sa, a_stride);
+            if (b != nullptr)
+                d += add_partials(0.0f, b + src * dm + i, Sb, b_stride);
+            v = fmaf(mult, d, v);
+            xr[i] = v;
+        }
+        row[i - c0] = v;
+        sum += v;
+    }
+    sum = block_sum(sum, red);
+    if (threadIdx.x < C)
+        cluster_write(&part_sum[rank], threadIdx.x, sum);
+    cluster_arrive();
+    cluster_wait();
+    float tot = 0.0f;
+#pragma unroll
+    for (int k = 0; k < C; k++)
+        tot += part_sum[k];
+    float mean = tot / (float)dm;
+    float sq = 0.0f;
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
+        float d = row[i - c0] - mean;
+        sq = fmaf(d, d, sq);
+    }
+    sq = block_sum(sq, red);
+    if (threadIdx.x < C)
+        cluster_write(&part_sq[rank], threadIdx.x, sq);
+    cluster_arrive();
+    cluster_wait();
+    tot = 0.0f;
+#pragma unroll
+    for (int k = 0; k < C; k++)
+        tot += part_sq[k];
+    float inv = 1.0f / sqrtf(tot / (float)dm + eps);
+    TO *o = out + (size_t)r * dm;
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x)
+        o[i] = from_f<TO>(fmaf((row[i - c0] - mean) * inv, w[i], bias != nullptr ? bias[i] : 0.0f));
+}
+
 }  // namespace jb
 
 using namespace jb;
@@ -76,6 +142,17 @@ extern "C" int jb_layernorm(float *x, const float *a, int Sa, long long a_stride
     if (dm <= 0 || dm > 49152 / 4 || (a == nullptr && b != nullptr) || (a != nullptr && row_idx != nullptr) ||
         (out != nullptr && w == nullptr) || (a != nullptr && Sa <= 0) || (b != nullptr && Sb <= 0))
         return JB_EINVAL;
+    // few rows of the bfloat16 path: a cluster of 8 CTAs per row (the 32-bit path keeps the
+    // one kernel whatever the batch, so that a row's bits do not depend on it)
+    constexpr int CL = 8;
+    if (out != nullptr && out_dt == JB_BF16 && n_out <= 32 && dm >= 64 * CL) {
+        int cols = (dm + CL - 1) / CL;
+        unsigned th = (unsigned)min(256, (cols + 31) / 32 * 32);
+        launch_cluster(layernorm_cluster_kernel<bf16, CL>, dim3((unsigned)n_out * CL), th, (size_t)cols * 4, st,
+                       CL, x, a, Sa, (size_t)a_stride, b, Sb, (size_t)b_stride, mult, row_idx, w, bias,
+                       (bf16 *)out, dm, cols, eps);
+        return launch_status();
+    }
     unsigned threads = (unsigned)min(256, (dm + 31) / 32 * 32);
     size_t smem = (size_t)dm * 4;
     if (out == nullptr || out_dt == JB_F32)

@@ -597,16 +597,17 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     out = torch.empty((nh, n, vd) if head_major else (n, nh, vd), dtype=q.dtype, device=q.device)
     L = lib()
     tc = (not force_simt and vd == hd and q.dtype == torch.bfloat16
-          and softcap == 0.0 and slopes is None and v_ld == 0 and not head_major
+          and v_ld == 0 and not head_major
           and (decode or blocks is not None) and bool(L.jb_attn_tc_ok(nh, nkv, hd))
           and (decode or head_scale is None or bool((head_scale > 0).all())))
     if tc and not decode:
         _need(blocks, "blocks", torch.int32, (None, 4))
-        _check(L.jb_attn_tc_prefill_sink(_p(q), _p(k_cache), _p(v_cache),
-                                         int(k_cache.shape[0]), _p(blocks),
-                                         blocks.shape[0], _p(block_table), block_table.shape[1],
-                                         _p(out), n, nh, nkv, hd, window, float(scale),
-                                         _p(head_scale), _p(sink), _stream()),
+        _check(L.jb_attn_tc_prefill_ext(_p(q), _p(k_cache), _p(v_cache),
+                                        int(k_cache.shape[0]), _p(blocks),
+                                        blocks.shape[0], _p(block_table), block_table.shape[1],
+                                        _p(out), n, nh, nkv, hd, window, float(scale),
+                                        _p(head_scale), _p(sink), float(softcap), _p(slopes),
+                                        _stream()),
                "attention (tcgen05, prefill)")
         return out
     if tc:
@@ -625,12 +626,12 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     for row0 in range(0, n, rows_per_call):
         cnt = min(rows_per_call, n - row0)
         if tc:
-            _check(L.jb_attn_tc_decode_scaled(_p(q), _p(k_cache), _p(v_cache),
-                                              int(k_cache.shape[0]), _p(row_pos),
-                                              _p(row_seq), _p(block_table), block_table.shape[1],
-                                              _p(scratch), n, row0, cnt, nh, nkv, hd, window,
-                                              float(scale), _p(head_scale), max_chunks, per_cta,
-                                              _stream()),
+            _check(L.jb_attn_tc_decode_ext(_p(q), _p(k_cache), _p(v_cache),
+                                           int(k_cache.shape[0]), _p(row_pos),
+                                           _p(row_seq), _p(block_table), block_table.shape[1],
+                                           _p(scratch), n, row0, cnt, nh, nkv, hd, window,
+                                           float(scale), _p(head_scale), float(softcap),
+                                           _p(slopes), max_chunks, per_cta, _stream()),
                    "attention (tcgen05, decode)")
             _check(L.jb_attention_merge_sink(_p(scratch), _p(row_pos), _p(out), _DT[q.dtype], row0,
                                              cnt, nh, hd, window, parts, per_cta, _p(sink),
@@ -790,6 +791,23 @@ def linear(a: torch.Tensor, weight: torch.Tensor, force_simt: bool = False,
     scratch = torch.empty((need,), dtype=torch.float32, device=a.device) if need else None
     _check(L.jb_gemm_simt(_p(a), _DT[a.dtype], _p(weight), _DT[weight.dtype], _p(out), n, m,
                           k, _p(scratch), _stream()), "linear", kernels=2 if need else 1)
+    return out
+
+
+def linear_heads(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """One product per head in one launch of the tensor-core kernel: a [H, n, k] . weight
+    [H m, k]^T, head h with rows h m .. of the weight.  Returns float32 [H, S, n, m].
+    bfloat16 operands whose rows are a multiple of 8 long only."""
+    _need(a, "activations", torch.bfloat16, (None, None, None))
+    H, n, k = a.shape
+    _need(weight, "weight", torch.bfloat16, (None, k))
+    if weight.shape[0] % H or k % 8:
+        raise KernelError("linear_heads: the weight's rows are no multiple of the heads, or k of 8")
+    m = weight.shape[0] // H
+    S = _splits(n, m, k, a.device.index)
+    out = torch.empty((H, S, n, m), dtype=torch.float32, device=a.device)
+    _check(lib().jb_gemm_tc_heads(_p(a), _p(weight), _p(out), n, m, k, S, H, _stream()),
+           "linear_heads (tcgen05)")
     return out
 
 

@@ -340,8 +340,7 @@ public:
         const int32_t *blocks = nullptr;
         int n_blocks = 0;
         if (!decode && ctx.dtype == BF16 && ops::attention_tc_ok(g_.nh, g_.nkv, g_.hd) && g_.vd == g_.hd &&
-            (!head_scale_ || g_.head_scale_positive) && !ctx.seq_len.empty() && g_.softcap == 0.0f &&
-            !has_slopes_) {
+            (!head_scale_ || g_.head_scale_positive) && !ctx.seq_len.empty()) {
             int per = ops::attention_block_positions(g_.nh, g_.nkv);
             std::string key = "attention_blocks/" + std::to_string(per);
             auto it = ctx.extras.find(key);

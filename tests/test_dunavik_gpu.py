@@ -79,6 +79,17 @@ def test_relu_squared(odt, n, ff, S, extra):
     assert (got[z.sum(0)[:, :ff] < 0] == 0).all()
 
 
+@pytest.mark.parametrize("H,n,k,m", [(4, 1, 16, 40), (3, 8, 64, 384), (2, 70, 96, 64), (5, 200, 384, 128),
+                                     (2, 300, 64, 200), (8, 1030, 128, 96)])
+def test_one_product_per_head_in_one_launch(H, n, k, m):
+    """Heads whose rows of activations and of weights are no multiple of any tile."""
+    a, w = bf(rnd(H, n, k, seed=1)), bf(rnd(H * m, k, seed=2) / k ** 0.5)
+    got = ops().linear_heads(a.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV)).sum(1).cpu()
+    assert ops().gemm_tc_error() == 0
+    want = torch.einsum("hnk,hmk->hnm", a, w.reshape(H, m, k))
+    assert (got - want).abs().max() <= 1e-4 * max(1.0, float(want.abs().max()))
+
+
 class Paged:
     """Rows of several sequences in pages that lie in no order."""
 
@@ -137,7 +148,7 @@ def test_query_temperature_and_append(dtype, nh, nkv, hd, vd, every):
 
 
 def run_window_attention(dtype, hd, vd, nh, nkv, lens, rows, window=0, cap=0.0, standout=(), seed=0,
-                         decode=False):
+                         decode=False, mode="plain"):
     """rows: per sequence, (first position, count) of the rows that ask.  standout: (sequence, key
     position, query position): that key is made to dominate that query's scores in the LAST head's
     group (the head whose slope is smallest)."""
@@ -166,9 +177,22 @@ def run_window_attention(dtype, hd, vd, nh, nkv, lens, rows, window=0, cap=0.0, 
     if window:
         max_chunks = min(max_chunks, (window - 1) // chunk + 2)
     slopes = torch.tensor([2.0 ** (-8.0 * (a + 1) / nh) for a in range(nh)], dtype=torch.float32)
+    kw = {}
+    if mode == "plain":
+        kw["force_simt"] = True
+    elif not decode:
+        # the tensor-core kernel for prompts: runs of consecutive positions
+        per = ops().attention_block_positions(nh, nkv)
+        r0, at = [], 0
+        for (p0, cnt) in rows:
+            r0.append(at)
+            at += cnt
+        kw["blocks"] = ops().attention_blocks(r0, [p for p, _ in rows], [c for _, c in rows], per,
+                                              torch.device(DEV))
     got = ops().attention(torch.cat(qs).to(dtype).to(DEV), kc, vc, row_pos.to(DEV), row_seq.to(DEV),
                           P.table.to(DEV), window, scale, max_chunks, decode=decode, softcap=cap,
-                          slopes=slopes.to(DEV)).float().cpu()
+                          slopes=slopes.to(DEV), **kw).float().cpu()
+    assert ops().attn_tc_error() == 0
     return got, torch.cat(want)
 
 
@@ -184,6 +208,19 @@ def test_capped_sloped_window_attention(dtype, hd, vd, nh, nkv, window, cap):
     got, want = run_window_attention(dtype, hd, vd, nh, nkv, lens, [(0, 1), (199, 1), (66, 1), (329, 1)],
                                      window, cap, seed=4, decode=True)
     close(got, want, dtype)
+
+
+@pytest.mark.parametrize("hd,nh,nkv,window,cap", [(64, 4, 1, 130, 50.0), (64, 10, 5, 0, 20.0), (128, 2, 2, 64, 8.0),
+                                                   (128, 8, 2, 1000, 0.0), (128, 40, 2, 37, 30.0)])
+def test_capped_sloped_window_attention_on_the_tensor_cores(hd, nh, nkv, window, cap):
+    dt = torch.bfloat16
+    lens = [1, 300, 131, 520]
+    got, want = run_window_attention(dt, hd, hd, nh, nkv, lens, [(0, 1), (0, 300), (100, 31), (0, 520)],
+                                     window, cap, seed=4, mode="tc")
+    close(got, want, dt, "prompt rows")
+    got, want = run_window_attention(dt, hd, hd, nh, nkv, lens, [(0, 1), (299, 1), (130, 1), (519, 1)],
+                                     window, cap, seed=5, decode=True, mode="tc")
+    close(got, want, dt, "decode rows")
 
 
 def test_the_cap_and_the_slopes_matter():
@@ -207,35 +244,39 @@ def test_the_cap_and_the_slopes_matter():
     assert 70.0 < float(got[0, 0, 0]) < 80.0 and 44.0 < float(got[0, 1, 0]) < 52.0
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+KERNELS = [(torch.float32, "plain", 32, 48), (torch.bfloat16, "plain", 32, 48), (torch.bfloat16, "tc", 64, 64),
+           (torch.bfloat16, "tc", 128, 128)]
+
+
+@pytest.mark.parametrize("dtype,mode,hd,vd", KERNELS)
 @pytest.mark.parametrize("decode", [False, True])
-def test_one_key_that_stands_out(dtype, decode):
+def test_one_key_that_stands_out(dtype, mode, hd, vd, decode):
     """A key far back, at a page's and a chunk's border, and the first one: made to dominate one
     query's scores in the head with the smallest slope, with a value that shows."""
     n = 900
     for kp, qp in [(3, 899), (0, 700), (63, 899), (64, 640), (127, 128), (128, 899), (767, 768), (512, 513)]:
         rows = [(qp, 1)] if decode else [(max(0, qp - 40), min(41, qp + 1))]
-        got, want = run_window_attention(dtype, 32, 48, 4, 2, [n], rows, 0, 50.0, standout=[(0, kp, qp)], seed=kp,
-                                         decode=decode)
+        got, want = run_window_attention(dtype, hd, vd, 4, 2, [n], rows, 0, 50.0, standout=[(0, kp, qp)], seed=kp,
+                                         decode=decode, mode=mode)
         assert want[-1, 3].mean() > 3.0           # the key does dominate its query there
         close(got, want, dtype, f"key {kp} query {qp}")
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,mode,hd,vd", KERNELS)
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("window", [1, 37, 64, 128, 200])
-def test_keys_at_a_windows_edge(dtype, decode, window):
+def test_keys_at_a_windows_edge(dtype, mode, hd, vd, decode, window):
     n = 600
     for qp in (window - 1, window, 300, 599):
         inside, outside = qp + 1 - window, qp - window
         rows = [(qp, 1)] if decode else [(max(0, qp - 20), min(21, qp + 1))]
-        got, want = run_window_attention(dtype, 32, 48, 4, 2, [n], rows, window, 50.0, standout=[(0, inside, qp)],
-                                         seed=qp, decode=decode)
+        got, want = run_window_attention(dtype, hd, vd, 4, 2, [n], rows, window, 50.0, standout=[(0, inside, qp)],
+                                         seed=qp, decode=decode, mode=mode)
         assert want[-1, 3].mean() > 3.0
         close(got, want, dtype, f"window {window} query {qp} inside")
         if outside >= 0:
-            got, want = run_window_attention(dtype, 32, 48, 4, 2, [n], rows, window, 50.0,
-                                             standout=[(0, outside, qp)], seed=qp, decode=decode)
+            got, want = run_window_attention(dtype, hd, vd, 4, 2, [n], rows, window, 50.0,
+                                             standout=[(0, outside, qp)], seed=qp, decode=decode, mode=mode)
             assert want[-1, 3].mean() < 2.0       # just outside: it must not show
             close(got, want, dtype, f"window {window} query {qp} outside")
 
