@@ -509,7 +509,8 @@ TensorMap tensors_from_json(Device &dev, const Json &tensors, const TensorList &
         if (shape != kv.second.shape) fail(JB_LLM_EOPEN, "tensor " + kv.first + ": unexpected shape");
         DType src = dtype_of(t.get("dtype"), F32);
         if (src != F32 && src != BF16) fail(JB_LLM_EOPEN, "tensor " + kv.first + ": float32 or bfloat16 is needed");
-        DType keep_as = compute == F32 ? F32 : src;
+        // small vectors of constants are float32 on the device whatever they come as
+        DType keep_as = compute == F32 || kv.second.kind == PARAM ? F32 : src;
         DevTensor d = dev.tensor(keep_as, shape);
         if (jb_convert(ptr_of<const void>(t.get("ptr")), src, d.ptr, keep_as, d.numel(), dev.stream) != 0)
             fail(JB_LLM_EFAIL, "tensor " + kv.first + ": the copy could not be launched");

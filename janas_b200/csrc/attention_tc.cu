@@ -641,19 +641,36 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 if constexpr (EXT) {
                     // every score goes through the cap and loses its head's slope times the
-                    // key's distance back: in log2 units, in place of the raw score
+                    // key's distance back: in log2 units, in place of the raw score.  Key
+                    // t0 + i is pos - t0 - i back: the slope's term is slope2 * i + sbase.
+                    const float sbase = slope2 * (float)(t0 - pos);
+                    const float k1 = c2 * inv_cap2;
+                    const bool capped = x.cap2 > 0.0f;
+                    if (inside && live) {
 #pragma unroll
-                    for (int i = 0; i < AT_KEYS; i += 4)
+                        for (int i = 0; i < AT_KEYS; i += 4)
 #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            int key = t0 + i + e;
-                            float v = -INFINITY;
-                            if (live && key <= pos && key >= lo)
-                                v = ext_score(__uint_as_float(raw[i + e]) * c2, x.cap2, inv_cap2, slope2,
-                                              pos - key);
-                            raw[i + e] = __float_as_uint(v);
-                            m4[e] = fmaxf(m4[e], v);
-                        }
+                            for (int e = 0; e < 4; e++) {
+                                float r = __uint_as_float(raw[i + e]);
+                                float bias = fmaf(slope2, (float)(i + e), sbase);
+                                float v = capped ? fmaf(x.cap2, fast_tanh(r * k1), bias) : fmaf(r, c2, bias);
+                                raw[i + e] = __float_as_uint(v);
+                                m4[e] = fmaxf(m4[e], v);
+                            }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < AT_KEYS; i += 4)
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                int key = t0 + i + e;
+                                float r = __uint_as_float(raw[i + e]);
+                                float bias = fmaf(slope2, (float)(i + e), sbase);
+                                float v = capped ? fmaf(x.cap2, fast_tanh(r * k1), bias) : fmaf(r, c2, bias);
+                                v = (live && key <= pos && key >= lo) ? v : -INFINITY;
+                                raw[i + e] = __float_as_uint(v);
+                                m4[e] = fmaxf(m4[e], v);
+                            }
+                    }
                 } else if (inside && live) {
 #pragma unroll
                     for (int i = 0; i < AT_KEYS; i += 4)

@@ -767,7 +767,8 @@ extern "C" int jb_qkv_bias_append_temp(const float *qkv, int S, long long stride
 {
     if (n <= 0)
         return JB_OK;
-    if (nh <= 0 || hd <= 0 || (append && (nkv <= 0 || vd <= 0 || !k_cache || !v_cache)))
+    // nh = 0 with append: the product holds keys and values alone
+    if (nh < 0 || (nh == 0 && !append) || hd <= 0 || (append && (nkv <= 0 || vd <= 0 || !k_cache || !v_cache)))
         return JB_EINVAL;
     int width = nh * hd + (append ? nkv * (hd + vd) : 0);
     if (ld < width)

@@ -105,6 +105,14 @@ int jb_latent_down(const float *P, int S, long long stride, int ld, int q_col0, 
                    const float *cs, const float *sn, int rot_half, const int32_t *row_pos,
                    const int32_t *row_seq, const int32_t *block_table, int bt_stride, void *cq_out,
                    void *k_cache, int cache_dt, int n, float eps, cudaStream_t st);
+int jb_latent_down_rows(const float *P, int S, long long stride, int ld, int q_col0, int q_rank,
+                        const float *wq, int kv_col0, int kv_rank, const float *wkv, int rot_dim,
+                        const float *cs, const float *sn, int rot_half, const int32_t *row_pos,
+                        const int32_t *row_seq, const int32_t *block_table, int bt_stride,
+                        void *cq_out, void *k_cache, void *rows_out, int cache_dt, int n, float eps,
+                        cudaStream_t st);
+int jb_gate_rows(const void *a, const float *g, int Sg, long long g_stride, int g_ld, int g_col0,
+                 void *out, int dt, int n, int width, cudaStream_t st);
 int jb_latent_q_split(const float *Q, int S, long long stride, int nh, int D, int R, int C,
                       const float *cs, const float *sn, int rot_half, const int32_t *row_pos,
                       void *q_plain, void *q_lat, int dt, int n, cudaStream_t st);

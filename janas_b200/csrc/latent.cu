@@ -34,7 +34,8 @@ latent_down_kernel(const float *__restrict__ P, int S, size_t stride, int ld, in
                    const float *__restrict__ wkv, int rot_dim, const float *__restrict__ cs,
                    const float *__restrict__ sn, int rot_half, const int32_t *__restrict__ row_pos,
                    const int32_t *__restrict__ row_seq, const int32_t *__restrict__ block_table,
-                   int bt_stride, TC *__restrict__ cq_out, TC *__restrict__ k_cache, float eps)
+                   int bt_stride, TC *__restrict__ cq_out, TC *__restrict__ k_cache,
+                   TC *__restrict__ rows_out, float eps)
 {
     extern __shared__ float buf[];      // q_rank + kv_rank + rot_dim sums of this row
     __shared__ float red[32];
@@ -66,9 +67,16 @@ latent_down_kernel(const float *__restrict__ P, int S, size_t stride, int ld, in
     }
     int hd = kv_rank + rot_dim;
     TC *dst = k_cache + ((size_t)page * PAGE + pos % PAGE) * hd;
+    // the same row once more, beside the other rows of the step (for a step that forms
+    // its keys and values per head from it), or nowhere
+    TC *dst2 = rows_out != nullptr ? rows_out + row * hd : nullptr;
     float inv = 1.0f / sqrtf(sc / (float)kv_rank + eps);
-    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x)
-        dst[i] = from_f<TC>(zc[i] * inv * wkv[i]);
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) {
+        TC v = from_f<TC>(zc[i] * inv * wkv[i]);
+        dst[i] = v;
+        if (dst2 != nullptr)
+            dst2[i] = v;
+    }
     for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
         float v = zr[i];
         if (i < 2 * rot_half) {
@@ -77,6 +85,8 @@ latent_down_kernel(const float *__restrict__ P, int S, size_t stride, int ld, in
             v = (i & 1) ? fmaf(v, c, other * s) : fmaf(v, c, -other * s);
         }
         dst[kv_rank + i] = from_f<TC>(v);
+        if (dst2 != nullptr)
+            dst2[kv_rank + i] = from_f<TC>(v);
     }
 }
 
@@ -99,7 +109,12 @@ __global__ void latent_q_split_kernel(const float *__restrict__ Q, int S, size_t
     pdl_wait();
     float v = add_partials(0.0f, Q + i, S, stride);
     if (e < D) {
-        q_plain[((size_t)h * n + row) * D + e] = from_f<TC>(v);
+        // one head's rows together, or (no q_plain) the value's own place in q_lat, whose
+        // rows are then [plain | rotated] and C is D
+        if (q_plain != nullptr)
+            q_plain[((size_t)h * n + row) * D + e] = from_f<TC>(v);
+        else
+            q_lat[(row * nh + h) * (size_t)(C + R) + e] = from_f<TC>(v);
         return;
     }
     int r = e - D;
@@ -150,6 +165,23 @@ __global__ void heads_gate_kernel(const float *__restrict__ A, int S, int nh, in
         v *= 1.0f / (1.0f + expf(-z));
     }
     out[i] = from_f<TC>(v);
+}
+
+// out = a * sigmoid(sum of the gate's partial sums), value by value over rows [n, width]
+template <typename TC>
+__global__ void gate_rows_kernel(const TC *__restrict__ a, const float *__restrict__ g, int Sg,
+                                 size_t g_stride, int g_ld, int g_col0, TC *__restrict__ out, int width,
+                                 size_t total)
+{
+    pdl_trigger();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total)
+        return;
+    size_t row = i / width;
+    int col = (int)(i - row * width);
+    pdl_wait();
+    float z = add_partials(0.0f, g + row * g_ld + g_col0 + col, Sg, g_stride);
+    out[i] = from_f<TC>(to_f(a[i]) * (1.0f / (1.0f + expf(-z))));
 }
 
 template <typename T>
@@ -237,6 +269,21 @@ extern "C" int jb_latent_down(const float *P, int S, long long stride, int ld, i
                               const int32_t *block_table, int bt_stride, void *cq_out,
                               void *k_cache, int cache_dt, int n, float eps, cudaStream_t st)
 {
+    return jb_latent_down_rows(P, S, stride, ld, q_col0, q_rank, wq, kv_col0, kv_rank, wkv, rot_dim, cs, sn,
+                               rot_half, row_pos, row_seq, block_table, bt_stride, cq_out, k_cache,
+                               nullptr, cache_dt, n, eps, st);
+}
+
+// The same; rows_out (or null): [n, kv_rank + rot_dim], the rows that go to the cache
+// once more, one after the other.
+extern "C" int jb_latent_down_rows(const float *P, int S, long long stride, int ld, int q_col0,
+                                   int q_rank, const float *wq, int kv_col0, int kv_rank,
+                                   const float *wkv, int rot_dim, const float *cs, const float *sn,
+                                   int rot_half, const int32_t *row_pos, const int32_t *row_seq,
+                                   const int32_t *block_table, int bt_stride, void *cq_out,
+                                   void *k_cache, void *rows_out, int cache_dt, int n, float eps,
+                                   cudaStream_t st)
+{
     if (n <= 0)
         return JB_OK;
     if (S <= 0 || q_rank < 0 || kv_rank <= 0 || rot_dim < 0 || 2 * rot_half > rot_dim ||
@@ -250,11 +297,11 @@ extern "C" int jb_latent_down(const float *P, int S, long long stride, int ld, i
     if (cache_dt == JB_F32)
         launch(latent_down_kernel<float>, n, 256, smem, st, P, S, (size_t)stride, ld, q_col0, q_rank, wq,
                kv_col0, kv_rank, wkv, rot_dim, cs, sn, rot_half, row_pos, row_seq, block_table,
-               bt_stride, (float *)cq_out, (float *)k_cache, eps);
+               bt_stride, (float *)cq_out, (float *)k_cache, (float *)rows_out, eps);
     else if (cache_dt == JB_BF16)
         launch(latent_down_kernel<bf16>, n, 256, smem, st, P, S, (size_t)stride, ld, q_col0, q_rank, wq,
                kv_col0, kv_rank, wkv, rot_dim, cs, sn, rot_half, row_pos, row_seq, block_table,
-               bt_stride, (bf16 *)cq_out, (bf16 *)k_cache, eps);
+               bt_stride, (bf16 *)cq_out, (bf16 *)k_cache, (bf16 *)rows_out, eps);
     else
         return JB_EINVAL;
     return launch_status();
@@ -322,6 +369,28 @@ extern "C" int jb_heads_gate(const float *A, int S, int nh, int Dv, const float 
     else if (out_dt == JB_BF16)
         launch(heads_gate_kernel<bf16>, blocks, 256, 0, st, A, S, nh, Dv, g, Sg, (size_t)g_stride, g_ld,
                g_col0, (bf16 *)out, n, total);
+    else
+        return JB_EINVAL;
+    return launch_status();
+}
+
+// a: [n, width] of type dt; g: a gate's sums [Sg, n, g_ld] whose columns g_col0.. are the
+// gate.  out [n, width] = a * sigmoid(sum g), of type dt.
+extern "C" int jb_gate_rows(const void *a, const float *g, int Sg, long long g_stride, int g_ld,
+                            int g_col0, void *out, int dt, int n, int width, cudaStream_t st)
+{
+    size_t total = (size_t)n * width;
+    if (total == 0)
+        return JB_OK;
+    if (g == nullptr || Sg <= 0 || g_col0 < 0 || g_col0 + width > g_ld)
+        return JB_EINVAL;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dt == JB_F32)
+        launch(gate_rows_kernel<float>, blocks, 256, 0, st, (const float *)a, g, Sg, (size_t)g_stride, g_ld,
+               g_col0, (float *)out, width, total);
+    else if (dt == JB_BF16)
+        launch(gate_rows_kernel<bf16>, blocks, 256, 0, st, (const bf16 *)a, g, Sg, (size_t)g_stride, g_ld,
+               g_col0, (bf16 *)out, width, total);
     else
         return JB_EINVAL;
     return launch_status();

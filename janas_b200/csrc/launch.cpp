@@ -189,25 +189,51 @@ Buf activation(Device &d, const Stack &z, long long ff, int kind, DType out_dt) 
 Buf latent_down(Device &d, const Stack &P, long long q_col0, long long q_rank, const float *wq,
                 long long kv_col0, long long kv_rank, const float *wkv, long long rot_dim, const float *cs,
                 const float *sn, int rot_half, const int32_t *row_pos, const int32_t *row_seq,
-                const AttnCache &c, float eps, DType out_dt) {
+                const AttnCache &c, float eps, DType out_dt, Buf *rows_out) {
     if (!c.k || !c.writes) fail(JB_LLM_EINVAL, "latent_down: no cache to write the latent to");
     if (c.dt != out_dt) fail(JB_LLM_EINVAL, "latent_down: the cache is of another type");
     Buf cq = d.pool.get(std::max<size_t>((size_t)P.n * (size_t)q_rank * dtype_size(out_dt), 16));
-    check(jb_latent_down(P.data(), P.S, P.stride(), as_int(P.m, "width"), (int)q_col0, (int)q_rank, wq,
-                         (int)kv_col0, (int)kv_rank, wkv, (int)rot_dim, cs, sn, rot_half, row_pos, row_seq,
-                         c.block_table, c.bt_stride, cq.ptr, c.k, out_dt, as_int(P.n, "rows"), eps, d.stream),
-          "latent_down");
+    if (rows_out) *rows_out = d.pool.get((size_t)P.n * (size_t)(kv_rank + rot_dim) * dtype_size(out_dt));
+    check(jb_latent_down_rows(P.data(), P.S, P.stride(), as_int(P.m, "width"), (int)q_col0, (int)q_rank, wq,
+                              (int)kv_col0, (int)kv_rank, wkv, (int)rot_dim, cs, sn, rot_half, row_pos,
+                              row_seq, c.block_table, c.bt_stride, cq.ptr, c.k,
+                              rows_out ? rows_out->ptr : nullptr, out_dt, as_int(P.n, "rows"), eps,
+                              d.stream), "latent_down");
     return cq;
 }
 
 Buf latent_q_split(Device &d, const Stack &Q, int nh, long long D, long long R, long long C, const float *cs,
-                   const float *sn, int rot_half, const int32_t *row_pos, void *q_lat, DType dt) {
+                   const float *sn, int rot_half, const int32_t *row_pos, void *q_lat, DType dt,
+                   bool plain_head_major) {
     if (Q.m != (long long)nh * (D + R)) fail(JB_LLM_EINVAL, "latent_q_split: the product is not heads x (plain + rotated) wide");
+    if (!plain_head_major && C != D) fail(JB_LLM_EINVAL, "latent_q_split: whole queries have their plain part first");
     resolve_bias(d, const_cast<Stack &>(Q));
-    Buf qp = d.pool.get((size_t)nh * (size_t)Q.n * (size_t)D * dtype_size(dt));
+    Buf qp;
+    if (plain_head_major) qp = d.pool.get((size_t)nh * (size_t)Q.n * (size_t)D * dtype_size(dt));
     check(jb_latent_q_split(Q.data(), Q.S, Q.stride(), nh, (int)D, (int)R, (int)C, cs, sn, rot_half, row_pos,
                             qp.ptr, q_lat, dt, as_int(Q.n, "rows"), d.stream), "latent_q_split");
     return qp;
+}
+
+void kv_append(Device &d, const Stack &kv, const int32_t *row_pos, const int32_t *row_seq, const AttnCache &c,
+               int kv_heads, int hd, int vd) {
+    if (kv.m < (long long)kv_heads * (hd + vd)) fail(JB_LLM_EINVAL, "kv_append: the product is narrower than k and v");
+    if (!c.k || !c.v) fail(JB_LLM_EINVAL, "kv_append: no pages to append to");
+    resolve_bias(d, const_cast<Stack &>(kv));
+    check(jb_qkv_bias_append_temp(kv.data(), kv.S, kv.stride(), as_int(kv.m, "width"), nullptr, row_pos, row_seq,
+                                  c.block_table, c.bt_stride, nullptr, c.k, c.v, c.dt, as_int(kv.n, "rows"), 0,
+                                  kv_heads, hd, vd, 1, 0.0f, 0, d.stream), "kv_append");
+}
+
+Buf gate_rows(Device &d, const void *a, DType dt, long long n, long long width, const Stack &g,
+              long long g_col0) {
+    need_float(dt, "gate_rows");
+    if (!g || g.n != n || g_col0 < 0 || g_col0 + width > g.m)
+        fail(JB_LLM_EINVAL, "gate_rows: the gate does not cover the rows");
+    Buf out = d.pool.get((size_t)n * (size_t)width * dtype_size(dt));
+    check(jb_gate_rows(a, g.data(), g.S, g.stride(), as_int(g.m, "width"), (int)g_col0, out.ptr, dt,
+                       as_int(n, "rows"), as_int(width, "width"), d.stream), "gate_rows");
+    return out;
 }
 
 void latent_q_join(Device &d, const HeadStack &A, long long R, void *q_lat, DType dt) {

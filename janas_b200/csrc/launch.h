@@ -172,12 +172,19 @@ Buf qkv_bias_append(Device &d, const Stack &qkv, const float *bias, const int32_
 Buf latent_down(Device &d, const Stack &P, long long q_col0, long long q_rank, const float *wq,
                 long long kv_col0, long long kv_rank, const float *wkv, long long rot_dim,
                 const float *cos, const float *sin, int rot_half, const int32_t *row_pos,
-                const int32_t *row_seq, const AttnCache &c, float eps, DType out_dt);
+                const int32_t *row_seq, const AttnCache &c, float eps, DType out_dt, Buf *rows_out = nullptr);
 // Q: the query product's sums [S, n, nh (D + R)] -> the plain parts [nh, n, D] (returned)
 // and the rotated parts in columns C.. of q_lat [n, nh, C + R]
 Buf latent_q_split(Device &d, const Stack &Q, int nh, long long D, long long R, long long C,
                    const float *cos, const float *sin, int rot_half, const int32_t *row_pos,
-                   void *q_lat, DType dt);
+                   void *q_lat, DType dt, bool plain_head_major = true);
+// A product that holds keys and values alone, [k | v] per row: into the cache pages at
+// the rows' positions (c.k, c.v, c.block_table; kv_heads heads of hd and vd values).
+void kv_append(Device &d, const Stack &kv, const int32_t *row_pos, const int32_t *row_seq,
+               const AttnCache &c, int kv_heads, int hd, int vd);
+// a [n, width] in dt, times sigmoid of the gate's sums (columns g_col0.. of g): [n, width] in dt
+Buf gate_rows(Device &d, const void *a, DType dt, long long n, long long width, const Stack &g,
+              long long g_col0);
 void latent_q_join(Device &d, const HeadStack &A, long long R, void *q_lat, DType dt);
 // per-head sums joined into rows [n, H m], times sigmoid of the gate's sums (columns
 // g_col0.. of g; an empty g: no gate)

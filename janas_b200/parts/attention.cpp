@@ -416,9 +416,17 @@ private:
 // applied to the weighted sum; the two per-head products are one product per head
 // over rows gathered head by head (ops::linear_heads).
 //
+// A step of whole prompts in bfloat16 whose per-head sizes the tensor-core attention
+// kernel takes (D + R = Dv = 64 or 128) forms keys and values per head after all,
+// for that step alone, in pages of its own: [Wuk_head c | kr] and Wuv_head c are one
+// product of the rows [c | kr] with a matrix made at load time (the heads' key and
+// value matrices with an identity for the shared part).  The cache gets the latents
+// as always, and decoding goes on from them.
+//
 // params: hidden_size, num_heads, head_dim (D), rot_dim (R), v_head_dim (Dv), kv_rank
-// (C), q_rank (Cq), scale, eps, gate (default true), position (a part, kind
-// rope_pairs), names (optional): dq, dq_norm, uq, dkv, dkv_norm, uk, uv, gate, o
+// (C), q_rank (Cq), scale, eps, gate (default true), per_head_prompts (default true:
+// false keeps prompts on the latents too), position (a part, kind rope_pairs), names
+// (optional): dq, dq_norm, uq, dkv, dkv_norm, uk, uv, gate, o
 class LatentAttention : public Mixer {
 public:
     LatentAttention(const PartSpec &s, DType dt, Device *d) : Mixer(s, dt, d) {
@@ -432,6 +440,7 @@ public:
         scale_ = (float)s.get_double("scale");
         eps_ = (float)s.get_double("eps");
         gate_ = s.has("gate") ? s.params.get("gate").as_bool() : true;
+        per_head_prompts_ = s.has("per_head_prompts") ? s.params.get("per_head_prompts").as_bool() : true;
         if (hidden_ <= 0 || H_ <= 0 || D_ <= 0 || R_ < 0 || Dv_ <= 0 || C_ <= 0 || Cq_ <= 0)
             config_error("latent_attention: sizes must be positive");
         if (C_ + R_ > 512)
@@ -490,9 +499,41 @@ public:
         w_uv_ = take(t, name(p, n_uv_));
         w_o_ = take(t, name(p, n_o_));
         position_->load(name(p, "position"), t);
+        if (per_head_prompts_ && dtype == BF16 && D_ + R_ == Dv_ && ops::attention_tc_ok(H_, H_, (int)Dv_) &&
+            w_uv_.dt == BF16 && w_ukT_.dt == BF16)
+            make_expander(take_back_uk());
+    }
+
+    // [H D, C] once more out of its transposed form (load() has given the original back)
+    DevTensor take_back_uk() {
+        DevTensor t = w_ukT_;
+        t.shape = {H_ * C_, D_};
+        return ops::transpose_heads(*dev, t, H_);     // [H, C, D] -> [H, D, C]
+    }
+
+    // Rows [c | kr] times this matrix are, head by head, [Wuk_head c | kr], and after
+    // all heads' keys the values Wuv c: [H (D + R) + H Dv, C + R].
+    void make_expander(const DevTensor &uk) {
+        size_t es = dtype_size(uk.dt);
+        long long W = C_ + R_, hd = D_ + R_;
+        w_expand_ = dev->tensor(uk.dt, {H_ * hd + H_ * Dv_, W}, true);
+        std::vector<uint16_t> eye((size_t)(R_ * R_), 0);
+        for (long long i = 0; i < R_; i++) eye[(size_t)(i * R_ + i)] = 0x3f80;      // 1.0 in bfloat16
+        char *dst = (char *)w_expand_.ptr;
+        for (int h = 0; h < H_; h++) {
+            cuda_check(cudaMemcpy2D(dst + (size_t)(h * hd) * W * es, W * es, (const char *)uk.ptr + (size_t)h * D_ * C_ * es,
+                                    C_ * es, C_ * es, D_, cudaMemcpyDeviceToDevice), "placing a head's key matrix");
+            if (R_ > 0)
+                cuda_check(cudaMemcpy2D(dst + ((size_t)(h * hd + D_) * W + C_) * es, W * es, eye.data(), R_ * es,
+                                        R_ * es, R_, cudaMemcpyHostToDevice), "placing the shared part's identity");
+        }
+        cuda_check(cudaMemcpy2D(dst + (size_t)(H_ * hd) * W * es, W * es, w_uv_.ptr, C_ * es, C_ * es, H_ * Dv_,
+                                cudaMemcpyDeviceToDevice), "placing the value matrices");
+        dev->sync();
     }
 
     size_t weight_bytes() const override {
+        // (the matrix a prompt step uses instead of uk and uv is not read by a decode step)
         return w_in_.bytes() + w_uq_.bytes() + w_ukT_.bytes() + w_uv_.bytes() + w_o_.bytes() +
                wq_norm_.bytes() + wc_norm_.bytes();
     }
@@ -519,6 +560,8 @@ public:
         long long n = ctx.n_rows;
         size_t esz = dtype_size(ctx.dtype);
         Stack P = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        if (w_expand_ && ctx.kind == PREFILL && ctx.dtype == BF16 && !ctx.captured && !ctx.seq_len.empty())
+            return forward_per_head(ctx, P, cache, rot_half);
         Buf cq = ops::latent_down(d, P, 0, Cq_, (const float *)wq_norm_.ptr, Cq_, C_,
                                   (const float *)wc_norm_.ptr, R_, position_->cos(), position_->sin(), rot_half,
                                   ctx.row_pos, ctx.row_seq, cache.kv, eps_, ctx.dtype);
@@ -541,11 +584,76 @@ public:
         return ops::linear(d, a.ptr, ctx.dtype, n, (long long)H_ * Dv_, w_o_);
     }
 
+    // Whole prompts on the tensor cores: keys and values per head, for this step alone.
+    Stack forward_per_head(StepContext &ctx, Stack &P, LayerCache &cache, int rot_half) {
+        Device &d = *ctx.dev;
+        long long n = ctx.n_rows;
+        int hd = (int)(D_ + R_);
+        Buf rows;
+        Buf cq = ops::latent_down(d, P, 0, Cq_, (const float *)wq_norm_.ptr, Cq_, C_,
+                                  (const float *)wc_norm_.ptr, R_, position_->cos(), position_->sin(), rot_half,
+                                  ctx.row_pos, ctx.row_seq, cache.kv, eps_, ctx.dtype, &rows);
+        // whole queries [n, H, D + R], the rotated part turned
+        Buf q = d.pool.get((size_t)n * (size_t)H_ * (size_t)hd * 2);
+        {
+            Stack Q = ops::linear(d, cq.ptr, ctx.dtype, n, Cq_, w_uq_);
+            ops::latent_q_split(d, Q, H_, D_, R_, D_, position_->cos(), position_->sin(), rot_half, ctx.row_pos,
+                                q.ptr, ctx.dtype, false);
+        }
+        // pages of this step's own: every sequence starts at position 0 and gets the pages
+        // it needs one after the other
+        std::vector<int32_t> table;
+        long long n_pages = 0, most = 0;
+        for (int i = 0; i < ctx.n_seqs; i++) most = std::max(most, pages_for(ctx.seq_len[(size_t)i]));
+        int stride = (int)((most + 7) / 8 * 8);
+        table.assign((size_t)ctx.n_seqs * (size_t)stride, -1);
+        for (int i = 0; i < ctx.n_seqs; i++)
+            for (long long p = 0; p < pages_for(ctx.seq_len[(size_t)i]); p++)
+                table[(size_t)i * (size_t)stride + (size_t)p] = (int32_t)n_pages++;
+        Buf bt = d.pool.get(std::max<size_t>(table.size() * 4, 16));
+        d.upload(bt.ptr, table.data(), table.size() * 4);
+        size_t page_vals = (size_t)H_ * PAGE * (size_t)hd;
+        Buf kp = d.pool.get((size_t)n_pages * page_vals * 2), vp = d.pool.get((size_t)n_pages * page_vals * 2);
+        // slots past a sequence's end are never seen but are multiplied by weights of 0
+        cuda_check(cudaMemsetAsync(kp.ptr, 0, kp.bytes, d.stream), "clearing a step's key pages");
+        cuda_check(cudaMemsetAsync(vp.ptr, 0, vp.bytes, d.stream), "clearing a step's value pages");
+        ops::AttnCache own;
+        own.k = kp.ptr;
+        own.v = vp.ptr;
+        own.n_pages = n_pages;
+        own.dt = BF16;
+        own.block_table = bt.as<int32_t>();
+        own.bt_stride = stride;
+        {
+            Stack kv = ops::linear(d, rows.ptr, ctx.dtype, n, C_ + R_, w_expand_);
+            ops::kv_append(d, kv, ctx.row_pos, ctx.row_seq, own, H_, hd, hd);
+        }
+        ops::AttnGeometry g;
+        g.nh = g.nkv = H_;
+        g.hd = g.vd = hd;
+        g.scale = scale_;
+        int per = ops::attention_block_positions(g.nh, g.nkv);
+        std::string key = "attention_blocks/" + std::to_string(per);
+        auto it = ctx.extras.find(key);
+        if (it == ctx.extras.end()) {
+            StepContext::Extra e;
+            e.buf = ops::attention_blocks(d, ctx.seq_row0.data(), ctx.seq_pos0.data(), ctx.seq_len.data(), ctx.n_seqs,
+                                          per, &e.n);
+            it = ctx.extras.emplace(key, std::move(e)).first;
+        }
+        int max_chunks = (int)(ctx.max_pos / chunk_ + 1);
+        Buf o = ops::attention(d, q.ptr, n, own, g, ctx.row_pos, ctx.row_seq, max_chunks,
+                               it->second.buf.as<int32_t>(), it->second.n, false);
+        Buf a = gate_ ? ops::gate_rows(d, o.ptr, ctx.dtype, n, (long long)H_ * Dv_, P, Cq_ + C_ + R_) : std::move(o);
+        return ops::linear(d, a.ptr, ctx.dtype, n, (long long)H_ * Dv_, w_o_);
+    }
+
     Json info() const override {
         Json o = Json::object();
         o.set("position", position_->info());
         o.set("position_kind", position_->spec.kind);
         o.set("gate", gate_);
+        o.set("per_head_prompts", (bool)w_expand_);
         return o;
     }
 
@@ -557,7 +665,8 @@ private:
     ops::AttnGeometry g_;
     std::unique_ptr<PositionEncoding> position_;
     std::string n_dq_, n_dqn_, n_uq_, n_dkv_, n_dkvn_, n_uk_, n_uv_, n_g_, n_o_;
-    DevTensor w_in_, wq_norm_, wc_norm_, w_uq_, w_ukT_, w_uv_, w_o_;
+    DevTensor w_in_, wq_norm_, wc_norm_, w_uq_, w_ukT_, w_uv_, w_o_, w_expand_;
+    bool per_head_prompts_ = true;
     int chunk_ = 0;
 };
 

@@ -54,9 +54,11 @@ DB = config(50, 101, [latent(3, 10, 6, 6, 22, 14, 0.3, base=77.0, dims=4, ff=70)
                       attn(6, 2, 24, 40, 0.2, window=200, ff=30),
                       attn(3, 3, 8, 8, 0.4)],
             (0, 2, 3), eps=1e-4, mult=1.0)
-# heads of 64 in one group, a window longer than a chunk; the latent mixer in the middle of the pass
+# heads of 64 in one group, a window longer than a chunk; the latent mixer in the middle of the pass,
+# its plain and rotated parts together as long as its values (64: whole prompts in bfloat16 then form
+# keys and values per head for the tensor-core kernel)
 DC = config(128, 300, [attn(4, 1, 64, 64, 0.11, window=130, softcap=50.0, q_temp=(0.4, 64), ff=200),
-                       latent(2, 64, 32, 64, 96, 48, 0.09, base=100000.0, ff=136),
+                       latent(2, 32, 32, 64, 96, 48, 0.09, base=100000.0, ff=136),
                        attn(4, 1, 64, 64, 0.13, window=130, softcap=50.0, q_temp=(0.4, 64), ff=72)],
             (1, 2, 2), eps=1e-5, mult=0.8)
 # heads of 128, as many key/value heads as heads, a window of exactly a page, a temperature that

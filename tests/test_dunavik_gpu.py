@@ -518,6 +518,36 @@ def test_batches_of_unequal_requests(name, dtype):
             assert np.array_equal(alone["r0"][p], got["b0r0"][p])
 
 
+def test_prompts_per_head_and_on_the_latents_agree():
+    """bfloat16 prompts of a latent mixer whose sizes the tensor-core kernel takes form keys and
+    values per head; with that turned off they run on the latents like every other step.  Both
+    agree with the plain model, and decoding goes on from the same cache."""
+    from janas_b200.config import config_from_dict
+    from janas_b200.engine import Engine
+    import dataclasses
+    name = "DC"
+    folder, c, w = model(name)
+    spec = config_from_dict(c).to_model_spec()
+    assert spec.layers[1].mixer.kind == "latent_attention"
+    layers = list(spec.layers)
+    m = layers[1].mixer
+    layers[1] = dataclasses.replace(layers[1], mixer=dataclasses.replace(m, params={**m.params, "per_head_prompts": False}))
+    slow = Engine.from_spec(dataclasses.replace(spec, layers=tuple(layers)),
+                            tensors={k: (v.to(torch.bfloat16) if v.dim() == 2 else v).to(DEV) for k, v in w.items()},
+                            dtype="bfloat16",
+                            max_tokens=2048)
+    reqs = [requests(name)[4], requests(name)[2], requests(name)[5]]
+    batch = [[(reqs[0], len(reqs[0]) - 30), (reqs[1], len(reqs[1])), (reqs[2], len(reqs[2]) - 70)]]
+    ids = [f"b0r{i}" for i in range(3)]
+    a = run_trace(slow, trace_batches(batch))
+    b = run_trace(engine(name, "bfloat16"), trace_batches(batch))
+    check(name, "bfloat16", a, reqs, ids)
+    check(name, "bfloat16", b, reqs, ids)
+    differ = max(float(np.abs(a[i][p] - b[i][p]).max()) for i, t in zip(ids, reqs) for p in range(len(t)))
+    assert differ > 0.0        # two ways of rounding: the same bits would mean one path ran twice
+    slow.close()
+
+
 def test_the_latent_cache_has_no_values_of_its_own():
     e = engine("DA", "bfloat16")
     groups = e.cache._op("describe")["groups"]
