@@ -245,6 +245,360 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
     }
 }
 
+// Rows of a mixer whose keys are one row per position for all heads, with the
+// values inside it (a latent: nkv = 1, v_cache = k_cache): one CTA per (row, chunk)
+// brings the chunk's rows into shared memory once and serves every head from there,
+// where the kernel above would fetch them once per group of four heads, key by key.
+//
+//   scores   thread (key j, half of the heads): q . k_j for four heads at a time, 16 bytes
+//            of the key per load (rows padded by 16 bytes: no bank conflicts)
+//   softmax  a warp per head: the chunk's maximum, weights and their sum
+//   values   a thread per (8 value columns, four heads): sum_j p_hj k_j[columns]
+//
+// The partials (m, l, sum p v) have the layout of the kernel above; the merge kernel
+// joins them.  bfloat16 only (the 32-bit path keeps one kernel for every kind of row).
+constexpr int LD_THREADS = 256;
+constexpr int LD_SMEM_MAX = 200 * 1024;     // bytes of shared memory it may be given
+
+__global__ void __launch_bounds__(LD_THREADS)
+latent_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ k_cache,
+                     const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                     const int32_t *__restrict__ block_table, int bt_stride, float *__restrict__ part,
+                     int row0, int nh, int hd, int vd, int window, float scale, int max_chunks)
+{
+    extern __shared__ __align__(16) uint8_t ld_smem[];
+    const int ks = hd + 8;                                   // a key row's stride in values
+    bf16 *Ks = reinterpret_cast<bf16 *>(ld_smem);            // [ATT_CHUNK][ks]
+    bf16 *Qs = Ks + (size_t)ATT_CHUNK * ks;                  // [nh][hd]
+    float *Ss = reinterpret_cast<float *>(Qs + (size_t)nh * hd);   // [nh][ATT_CHUNK] scores, then weights
+    pdl_trigger();
+    pdl_wait();
+    int lrow = blockIdx.x / max_chunks, ci = blockIdx.x % max_chunks;
+    int row = row0 + lrow;
+    int pos = row_pos[row];
+    int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+    int c = lo / ATT_CHUNK + ci;
+    if (c > pos / ATT_CHUNK)
+        return;
+    int t0 = max(lo, c * ATT_CHUNK), t1 = min(pos, c * ATT_CHUNK + ATT_CHUNK - 1);
+    int nk = t1 - t0 + 1;
+    const int32_t *bt = block_table + (size_t)row_seq[row] * bt_stride;
+    int tid = threadIdx.x;
+    const int pieces = hd / 8;                               // 16-byte pieces of a row
+    // the chunk's rows and the row's queries into shared memory
+    for (int i = tid; i < nk * pieces; i += LD_THREADS) {
+        int j = i / pieces, pc = i - j * pieces;
+        int t = t0 + j;
+        const bf16 *src = k_cache + ((size_t)bt[t / PAGE] * PAGE + (t % PAGE)) * hd + pc * 8;
+        *reinterpret_cast<uint4 *>(Ks + (size_t)j * ks + pc * 8) = *reinterpret_cast<const uint4 *>(src);
+    }
+    for (int i = tid; i < nh * pieces; i += LD_THREADS)
+        reinterpret_cast<uint4 *>(Qs)[i] = reinterpret_cast<const uint4 *>(q + (size_t)row * nh * hd)[i];
+    __syncthreads();
+    // ---- scores
+    {
+        int j = tid % ATT_CHUNK, half = tid / ATT_CHUNK;     // two threads per key
+        int per_half = (nh + 1) / 2;
+        int h_begin = half * per_half, h_end = min(nh, h_begin + per_half);
+        const bf16 *kr = Ks + (size_t)j * ks;
+        for (int h = h_begin; h < h_end; h += 4) {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (j < nk) {
+                for (int pc = 0; pc < pieces; pc++) {
+                    float kv[8];
+                    uint4 kw = *reinterpret_cast<const uint4 *>(kr + pc * 8);
+                    uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        kv[2 * e] = __uint_as_float(w[e] << 16);
+                        kv[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        if (h + u < h_end) {
+                            uint4 qw = *reinterpret_cast<const uint4 *>(Qs + (size_t)(h + u) * hd + pc * 8);
+                            uint32_t x[4] = {qw.x, qw.y, qw.z, qw.w};
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                acc[u] = fmaf(__uint_as_float(x[e] << 16), kv[2 * e], acc[u]);
+                                acc[u] = fmaf(__uint_as_float(x[e] & 0xffff0000u), kv[2 * e + 1], acc[u]);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (h + u < h_end)
+                    Ss[(size_t)(h + u) * ATT_CHUNK + j] = j < nk ? acc[u] * scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+    // ---- a warp per head: maximum, weights, sum
+    {
+        int warp = tid >> 5, lane = tid & 31;
+        for (int h = warp; h < nh; h += LD_THREADS / 32) {
+            float *sr = Ss + (size_t)h * ATT_CHUNK;
+            float v[ATT_CHUNK / 32], m = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < ATT_CHUNK / 32; u++) {
+                v[u] = sr[lane + 32 * u];
+                m = fmaxf(m, v[u]);
+            }
+            m = warp_max(m);
+            float l = 0.0f;
+#pragma unroll
+            for (int u = 0; u < ATT_CHUNK / 32; u++) {
+                float p = expf(v[u] - m);          // 0 for the keys beyond the range (-inf)
+                sr[lane + 32 * u] = p;
+                l += p;
+            }
+            l = warp_sum(l);
+            if (lane == 0) {
+                float *dst = part + part_at((size_t)lrow, nh, h, max_chunks, ci, vd);
+                dst[0] = m;
+                dst[1] = l;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- values: the first vd entries of the same rows
+    {
+        int vp = vd / 8;
+        int groups = (nh + 3) / 4;
+        for (int item = tid; item < vp * groups; item += LD_THREADS) {
+            int hg = item / vp, pc = item - hg * vp;
+            int h = hg * 4;
+            float acc[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+                    acc[u][e] = 0.0f;
+            for (int j = 0; j < nk; j++) {
+                uint4 kw = *reinterpret_cast<const uint4 *>(Ks + (size_t)j * ks + pc * 8);
+                uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
+                float kv[8];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    kv[2 * e] = __uint_as_float(w[e] << 16);
+                    kv[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    float p = h + u < nh ? Ss[(size_t)(h + u) * ATT_CHUNK + j] : 0.0f;
+#pragma unroll
+                    for (int e = 0; e < 8; e++)
+                        acc[u][e] = fmaf(p, kv[e], acc[u][e]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (h + u >= nh)
+                    continue;
+                float *dst = part + part_at((size_t)lrow, nh, h + u, max_chunks, ci, vd) + 2 + pc * 8;
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+                    dst[e] = acc[u][e];
+            }
+        }
+    }
+}
+
+// The same with the two products on the tensor cores (warp-level mma, bfloat16 in, float
+// out), for rows of a multiple of 16 values:
+//
+//   scores   S[h][j] = q_h . k_j: warp w has the keys 16 w .. 16 w + 15 and every head
+//   softmax  a warp per head, as above; the weights also as bfloat16 [head][key]
+//   values   O[h][c] = sum_j p_hj k_j[c]: the warps share the value columns, 16 at a time
+//
+// Heads are padded to a multiple of 16 with rows of zeros, keys beyond the row's range are
+// rows of zeros with weight 0.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p)
+{
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *p)
+{
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                 "{%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(LD_THREADS)
+latent_decode_mma_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ k_cache,
+                         const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                         const int32_t *__restrict__ block_table, int bt_stride,
+                         float *__restrict__ part, int row0, int nh, int hd, int vd, int window,
+                         float scale, int max_chunks)
+{
+    extern __shared__ __align__(16) uint8_t ld_smem[];
+    const int ks = hd + 8;                                   // row strides, in values: 16 bytes of padding
+    const int nh16 = (nh + 15) / 16 * 16;
+    const int ps = ATT_CHUNK + 8;
+    bf16 *Ks = reinterpret_cast<bf16 *>(ld_smem);            // [ATT_CHUNK][ks]
+    bf16 *Qs = Ks + (size_t)ATT_CHUNK * ks;                  // [nh16][ks]
+    bf16 *Ps = Qs + (size_t)nh16 * ks;                       // [nh16][ps] weights
+    float *Ss = reinterpret_cast<float *>(Ps + (size_t)nh16 * ps);   // [nh][ATT_CHUNK] scores
+    pdl_trigger();
+    pdl_wait();
+    int lrow = blockIdx.x / max_chunks, ci = blockIdx.x % max_chunks;
+    int row = row0 + lrow;
+    int pos = row_pos[row];
+    int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+    int c = lo / ATT_CHUNK + ci;
+    if (c > pos / ATT_CHUNK)
+        return;
+    int t0 = max(lo, c * ATT_CHUNK), t1 = min(pos, c * ATT_CHUNK + ATT_CHUNK - 1);
+    int nk = t1 - t0 + 1;
+    const int32_t *bt = block_table + (size_t)row_seq[row] * bt_stride;
+    int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pieces = hd / 8;
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    // asynchronous copies, all in flight at once: the chunk's rows and the queries
+    auto copy16 = [](void *dst, const void *src) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)),
+                     "l"(src) : "memory");
+    };
+    for (int i = tid; i < ATT_CHUNK * pieces; i += LD_THREADS) {
+        int j = i / pieces, pc = i - j * pieces;
+        bf16 *dst = Ks + (size_t)j * ks + pc * 8;
+        if (j < nk) {
+            int t = t0 + j;
+            copy16(dst, k_cache + ((size_t)bt[t / PAGE] * PAGE + (t % PAGE)) * hd + pc * 8);
+        } else {
+            *reinterpret_cast<uint4 *>(dst) = zero4;
+        }
+    }
+    for (int i = tid; i < nh16 * pieces; i += LD_THREADS) {
+        int h = i / pieces, pc = i - h * pieces;
+        bf16 *dst = Qs + (size_t)h * ks + pc * 8;
+        if (h < nh)
+            copy16(dst, q + ((size_t)row * nh + h) * hd + pc * 8);
+        else
+            *reinterpret_cast<uint4 *>(dst) = zero4;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    // ---- scores: this warp's 16 keys against 16 heads at a time
+    {
+        int j0 = warp * 16;
+        // the lanes' rows for ldmatrix: A (heads x k) and B (keys x k, two tiles of 8 keys)
+        int a_row = lane & 15, a_k = (lane >> 4) * 8;
+        int b_row = (lane & 7) + (lane >> 4) * 8, b_k = ((lane >> 3) & 1) * 8;
+        for (int h0 = 0; h0 < nh16; h0 += 16) {
+            float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+            for (int k0 = 0; k0 < hd; k0 += 16) {
+                uint32_t a[4], b[4];
+                ldmatrix_x4(a, Qs + (size_t)(h0 + a_row) * ks + k0 + a_k);
+                ldmatrix_x4(b, Ks + (size_t)(j0 + b_row) * ks + k0 + b_k);
+                mma_bf16(acc[0], a, b[0], b[1]);
+                mma_bf16(acc[1], a, b[2], b[3]);
+            }
+#pragma unroll
+            for (int t = 0; t < 2; t++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    int h = h0 + (lane >> 2) + (e >> 1) * 8;
+                    int j = j0 + t * 8 + (lane & 3) * 2 + (e & 1);
+                    if (h < nh)
+                        Ss[(size_t)h * ATT_CHUNK + j] = j < nk ? acc[t][e] * scale : -INFINITY;
+                }
+        }
+    }
+    __syncthreads();
+    // ---- a warp per head: maximum, weights, sum
+    for (int h = warp; h < nh16; h += LD_THREADS / 32) {
+        bf16 *pr = Ps + (size_t)h * ps;
+        if (h >= nh) {
+            // a padding head's weights are zeros
+#pragma unroll
+            for (int u = 0; u < ATT_CHUNK / 32; u++)
+                pr[lane + 32 * u] = __float2bfloat16_rn(0.0f);
+            continue;
+        }
+        const float *sr = Ss + (size_t)h * ATT_CHUNK;
+        float v[ATT_CHUNK / 32], m = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < ATT_CHUNK / 32; u++) {
+            v[u] = sr[lane + 32 * u];
+            m = fmaxf(m, v[u]);
+        }
+        m = warp_max(m);
+        float l = 0.0f;
+#pragma unroll
+        for (int u = 0; u < ATT_CHUNK / 32; u++) {
+            // the weight as the product below sees it: the sum is of the rounded weights
+            bf16 pb = __float2bfloat16_rn(expf(v[u] - m));
+            pr[lane + 32 * u] = pb;
+            l += __bfloat162float(pb);
+        }
+        l = warp_sum(l);
+        if (lane == 0) {
+            float *dst = part + part_at((size_t)lrow, nh, h, max_chunks, ci, vd);
+            dst[0] = m;
+            dst[1] = l;
+        }
+    }
+    __syncthreads();
+    // ---- values: 16 columns at a time per warp, 16 heads at a time
+    {
+        int a_row = lane & 15, a_k = (lane >> 4) * 8;
+        int b_row = (lane & 7) + ((lane >> 3) & 1) * 8, b_c = (lane >> 4) * 8;
+        for (int c0 = warp * 16; c0 < vd; c0 += (LD_THREADS / 32) * 16) {
+            for (int h0 = 0; h0 < nh16; h0 += 16) {
+                float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+#pragma unroll
+                for (int j0 = 0; j0 < ATT_CHUNK; j0 += 16) {
+                    uint32_t a[4], b[4];
+                    ldmatrix_x4(a, Ps + (size_t)(h0 + a_row) * ps + j0 + a_k);
+                    ldmatrix_x4_trans(b, Ks + (size_t)(j0 + b_row) * ks + c0 + b_c);
+                    mma_bf16(acc[0], a, b[0], b[1]);
+                    mma_bf16(acc[1], a, b[2], b[3]);
+                }
+#pragma unroll
+                for (int t = 0; t < 2; t++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        int h = h0 + (lane >> 2) + (e >> 1) * 8;
+                        int cc = c0 + t * 8 + (lane & 3) * 2 + (e & 1);
+                        if (h < nh)
+                            part[part_at((size_t)lrow, nh, h, max_chunks, ci, vd) + 2 + cc] = acc[t][e];
+                    }
+            }
+        }
+    }
+}
+
+static size_t latent_decode_mma_smem(int nh, int hd, int vd)
+{
+    if (hd % 16 || vd % 16 || vd > hd || nh <= 0)
+        return 0;
+    size_t nh16 = (size_t)(nh + 15) / 16 * 16;
+    size_t bytes = (size_t)ATT_CHUNK * (hd + 8) * 2 + nh16 * (hd + 8) * 2 + nh16 * (ATT_CHUNK + 8) * 2 +
+                   (size_t)nh * ATT_CHUNK * 4;
+    return bytes <= (size_t)LD_SMEM_MAX ? bytes : 0;
+}
+
+// Bytes of shared memory the kernel above needs, or 0 where it does not take the sizes.
+static size_t latent_decode_smem(int nh, int hd, int vd)
+{
+    if (hd % 8 || vd % 8 || vd > hd || nh <= 0)
+        return 0;
+    size_t bytes = (size_t)ATT_CHUNK * (hd + 8) * 2 + (size_t)nh * hd * 2 + (size_t)nh * ATT_CHUNK * 4;
+    return bytes <= (size_t)LD_SMEM_MAX ? bytes : 0;
+}
+
 // N partials of one (row, head), fetched together, join the running (m, l, o):
 // their largest maximum first, then each weighted by e^(its maximum - that), so
 // that the weights do not wait for one another.  The sums run in chunk order.
@@ -429,6 +783,32 @@ extern "C" int jb_attention_ext(const void *q, const void *k_cache, const void *
                                       bt_stride, scratch, (float *)out, row0, n_rows, nh, nkv, hd,
                                       vd, window, scale, head_scale, sink, max_chunks, v_ld, softcap,
                                       slopes, head_major_rows, st);
+    // few rows over rows that are key and value at once for all heads: the chunk is
+    // brought into shared memory once for all heads
+    size_t ld_bytes = latent_decode_smem(nh, hd, vd);
+    if (dt == JB_BF16 && nkv == 1 && v_cache == k_cache && v_ld == hd && head_scale == nullptr &&
+        softcap == 0.0f && slopes == nullptr && ld_bytes > 0 &&
+        (uintptr_t)q % 16 == 0 && (uintptr_t)k_cache % 16 == 0) {
+        static unsigned long long smem_allowed = 0, mma_allowed = 0;
+        size_t mma_bytes = latent_decode_mma_smem(nh, hd, vd);
+        // said once per device, for the most the kernels may ever ask for
+        if (!allow_dynamic_smem(latent_decode_kernel, LD_SMEM_MAX, smem_allowed) ||
+            !allow_dynamic_smem(latent_decode_mma_kernel, LD_SMEM_MAX, mma_allowed))
+            return JB_ELAUNCH;
+        if (mma_bytes > 0)
+            launch(latent_decode_mma_kernel, dim3((unsigned)n_rows * max_chunks), LD_THREADS, mma_bytes, st,
+                   (const bf16 *)q, (const bf16 *)k_cache, row_pos, row_seq, block_table, bt_stride, scratch,
+                   row0, nh, hd, vd, window, scale, max_chunks);
+        else
+            launch(latent_decode_kernel, dim3((unsigned)n_rows * max_chunks), LD_THREADS, ld_bytes, st,
+                   (const bf16 *)q, (const bf16 *)k_cache, row_pos, row_seq, block_table, bt_stride, scratch,
+                   row0, nh, hd, vd, window, scale, max_chunks);
+        if (cudaGetLastError() != cudaSuccess)
+            return JB_ELAUNCH;
+        launch(attn_merge_kernel<bf16>, dim3(n_rows, nh), (vd + 31) / 32 * 32, 0, st, (const float *)scratch,
+               row_pos, (bf16 *)out, row0, nh, vd, window, max_chunks, 1, sink, head_major_rows);
+        return launch_status();
+    }
     if (dt == JB_BF16)
         return attention_typed<bf16>((const bf16 *)q, (const bf16 *)k_cache,
                                      (const bf16 *)v_cache, row_pos, row_seq, block_table,

@@ -59,6 +59,23 @@ layernorm_kernel(float *__restrict__ x, const float *__restrict__ a, int Sa, siz
         o[i] = from_f<TO>(fmaf((row[i] - mean) * inv, w[i], bias != nullptr ? bias[i] : 0.0f));
 }
 
+// The add alone, a thread per value: x += m * (sum a + sum b).  The order of the additions
+// is the norm kernels' own, so a value's bits do not depend on which kernel added it.
+__global__ void scaled_add_kernel(float *__restrict__ x, const float *__restrict__ a, int Sa, size_t a_stride,
+                                  const float *__restrict__ b, int Sb, size_t b_stride, float mult,
+                                  size_t total)
+{
+    pdl_trigger();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total)
+        return;
+    pdl_wait();
+    float d = add_partials(0.0f, a + i, Sa, a_stride);
+    if (b != nullptr)
+        d += add_partials(0.0f, b + i, Sb, b_stride);
+    x[i] = fmaf(mult, d, x[i]);
+}
+
 // The same for few rows of the bfloat16 path: a cluster of C CTAs per row, each with a
 // slice of `cols` columns, so that the partial sums a decode step's products leave (many
 // per value) are fetched by many threads at once.  The two sums cross the cluster through
@@ -142,6 +159,12 @@ extern "C" int jb_layernorm(float *x, const float *a, int Sa, long long a_stride
     if (dm <= 0 || dm > 49152 / 4 || (a == nullptr && b != nullptr) || (a != nullptr && row_idx != nullptr) ||
         (out != nullptr && w == nullptr) || (a != nullptr && Sa <= 0) || (b != nullptr && Sb <= 0))
         return JB_EINVAL;
+    if (out == nullptr && a != nullptr) {
+        size_t total = (size_t)n_out * dm;
+        launch(scaled_add_kernel, (unsigned)((total + 255) / 256), 256, 0, st, x, a, Sa, (size_t)a_stride, b, Sb,
+               (size_t)b_stride, mult, total);
+        return launch_status();
+    }
     // few rows of the bfloat16 path: a cluster of 8 CTAs per row (the 32-bit path keeps the
     // one kernel whatever the batch, so that a row's bits do not depend on it)
     constexpr int CL = 8;
