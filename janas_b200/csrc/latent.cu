@@ -28,7 +28,7 @@
 namespace jb {
 
 template <typename TC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 latent_down_kernel(const float *__restrict__ P, int S, size_t stride, int ld, int q_col0, int q_rank,
                    const float *__restrict__ wq, int kv_col0, int kv_rank,
                    const float *__restrict__ wkv, int rot_dim, const float *__restrict__ cs,
@@ -127,6 +127,59 @@ __global__ void latent_q_split_kernel(const float *__restrict__ Q, int S, size_t
     q_lat[(row * nh + h) * (size_t)(C + R) + C + r] = from_f<TC>(v);
 }
 
+// p[0] + p[stride] + ... for four neighbouring values at once
+__device__ __forceinline__ float4 sum4(const float *__restrict__ p, int S, size_t stride)
+{
+    float4 v = load4(p);
+    for (int s = 1; s < S; s++) {
+        float4 w = load4(p + (size_t)s * stride);
+        v = make_float4(v.x + w.x, v.y + w.y, v.z + w.z, v.w + w.w);
+    }
+    return v;
+}
+
+// latent_q_split with four neighbouring values of a head per thread (D, R and C multiples
+// of four: the four lie in the plain or in the rotated part, and hold whole pairs)
+template <typename TC>
+__global__ void latent_q_split_vec_kernel(const float *__restrict__ Q, int S, size_t stride, int nh, int D,
+                                          int R, int C, const float *__restrict__ cs,
+                                          const float *__restrict__ sn, int rot_half,
+                                          const int32_t *__restrict__ row_pos, TC *__restrict__ q_plain,
+                                          TC *__restrict__ q_lat, int n, size_t total4)
+{
+    pdl_trigger();
+    size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i4 >= total4)
+        return;
+    int per = D + R;
+    size_t i = i4 * 4;
+    size_t row = i / ((size_t)nh * per);
+    int rem = (int)(i - row * (size_t)nh * per);
+    int h = rem / per, e = rem - h * per;
+    int pos = row_pos[row];
+    pdl_wait();
+    float4 v = sum4(Q + i, S, stride);
+    if (e < D) {
+        if (q_plain != nullptr)
+            store4(q_plain + ((size_t)h * n + row) * D + e, v);
+        else
+            store4(q_lat + (row * nh + h) * (size_t)(C + R) + e, v);
+        return;
+    }
+    int r = e - D;
+    float o[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int u = 0; u < 4; u += 2) {
+        if (r + u < 2 * rot_half) {
+            float c = cs[(size_t)pos * rot_half + (r + u) / 2], s = sn[(size_t)pos * rot_half + (r + u) / 2];
+            float a = o[u], b = o[u + 1];
+            o[u] = fmaf(a, c, -b * s);
+            o[u + 1] = fmaf(b, c, a * s);
+        }
+    }
+    store4(q_lat + (row * nh + h) * (size_t)(C + R) + C + r, make_float4(o[0], o[1], o[2], o[3]));
+}
+
 template <typename TC>
 __global__ void latent_q_join_kernel(const float *__restrict__ A, int S, int nh, int C, int R,
                                      TC *__restrict__ q_lat, int n, size_t total)
@@ -182,6 +235,25 @@ __global__ void gate_rows_kernel(const TC *__restrict__ a, const float *__restri
     pdl_wait();
     float z = add_partials(0.0f, g + row * g_ld + g_col0 + col, Sg, g_stride);
     out[i] = from_f<TC>(to_f(a[i]) * (1.0f / (1.0f + expf(-z))));
+}
+
+// gate_rows with four neighbouring values per thread
+template <typename TC>
+__global__ void gate_rows_vec_kernel(const TC *__restrict__ a, const float *__restrict__ g, int Sg,
+                                     size_t g_stride, int g_ld, int g_col0, TC *__restrict__ out, int width,
+                                     size_t total4)
+{
+    pdl_trigger();
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= total4 * 4)
+        return;
+    size_t row = i / width;
+    int col = (int)(i - row * width);
+    pdl_wait();
+    float4 z = sum4(g + row * g_ld + g_col0 + col, Sg, g_stride);
+    float4 v = load4(a + i);
+    store4(out + i, make_float4(v.x / (1.0f + expf(-z.x)), v.y / (1.0f + expf(-z.y)), v.z / (1.0f + expf(-z.z)),
+                                v.w / (1.0f + expf(-z.w))));
 }
 
 template <typename T>
@@ -320,6 +392,19 @@ extern "C" int jb_latent_q_split(const float *Q, int S, long long stride, int nh
     if (S <= 0 || D <= 0 || R < 0 || C <= 0 || 2 * rot_half > R ||
         (rot_half > 0 && (cs == nullptr || sn == nullptr)))
         return JB_EINVAL;
+    size_t esz = dt == JB_F32 ? 4 : 2;
+    if (D % 4 == 0 && R % 4 == 0 && C % 4 == 0 && stride % 4 == 0 && (uintptr_t)Q % 16 == 0 &&
+        (uintptr_t)q_plain % (4 * esz) == 0 && (uintptr_t)q_lat % (4 * esz) == 0 && (dt == JB_F32 || dt == JB_BF16)) {
+        size_t total4 = total / 4;
+        unsigned vb = (unsigned)((total4 + 255) / 256);
+        if (dt == JB_F32)
+            launch(latent_q_split_vec_kernel<float>, vb, 256, 0, st, Q, S, (size_t)stride, nh, D, R, C, cs, sn,
+                   rot_half, row_pos, (float *)q_plain, (float *)q_lat, n, total4);
+        else
+            launch(latent_q_split_vec_kernel<bf16>, vb, 256, 0, st, Q, S, (size_t)stride, nh, D, R, C, cs, sn,
+                   rot_half, row_pos, (bf16 *)q_plain, (bf16 *)q_lat, n, total4);
+        return launch_status();
+    }
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (dt == JB_F32)
         launch(latent_q_split_kernel<float>, blocks, 256, 0, st, Q, S, (size_t)stride, nh, D, R, C, cs, sn,
@@ -384,6 +469,19 @@ extern "C" int jb_gate_rows(const void *a, const float *g, int Sg, long long g_s
         return JB_OK;
     if (g == nullptr || Sg <= 0 || g_col0 < 0 || g_col0 + width > g_ld)
         return JB_EINVAL;
+    size_t esz = dt == JB_F32 ? 4 : 2;
+    if (width % 4 == 0 && g_ld % 4 == 0 && g_col0 % 4 == 0 && g_stride % 4 == 0 && (uintptr_t)g % 16 == 0 &&
+        (uintptr_t)a % (4 * esz) == 0 && (uintptr_t)out % (4 * esz) == 0 && (dt == JB_F32 || dt == JB_BF16)) {
+        size_t total4 = total / 4;
+        unsigned vb = (unsigned)((total4 + 255) / 256);
+        if (dt == JB_F32)
+            launch(gate_rows_vec_kernel<float>, vb, 256, 0, st, (const float *)a, g, Sg, (size_t)g_stride, g_ld,
+                   g_col0, (float *)out, width, total4);
+        else
+            launch(gate_rows_vec_kernel<bf16>, vb, 256, 0, st, (const bf16 *)a, g, Sg, (size_t)g_stride, g_ld,
+                   g_col0, (bf16 *)out, width, total4);
+        return launch_status();
+    }
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (dt == JB_F32)
         launch(gate_rows_kernel<float>, blocks, 256, 0, st, (const float *)a, g, Sg, (size_t)g_stride, g_ld,
