@@ -417,10 +417,10 @@ def dunavik_cfg(size, n_layers, vocab, mixers="mixed", window=1024):
             layers.append({"type": "latent_attention", "mixer": m, "mlp": {"ff": ff, "kind": "dense"}})
         else:
             m = {"dim": hd, "heads": nh, "kv_heads": nkv, "mask": {"size": window},
-                 "q_temp": {"coef": 0.1, "every": 512}, "scale": hd ** -0.5, "softcap": 30.0, "vdim": hd}
+                 "q_temp": {"coef": 0.1, "every": 512}, "scale": hd ** -0.5, "softcap": 50.0, "vdim": hd}
             layers.append({"type": "attention", "mixer": m, "mlp": {"ff": ff, "kind": "dense"}})
     return {"architecture": "Dunavik", "layers": layers, "loop": {"start": 0, "stop": 0, "times": 1},
-            "norm": {"eps": 1e-5}, "residual_mult": 0.7, "vocab": vocab, "width": dm}
+            "norm": {"eps": 1e-5}, "residual_mult": 0.5, "vocab": vocab, "width": dm}
 
 
 def dunavik_flops(cfg, tokens, window):

@@ -27,8 +27,10 @@
 
 namespace jb {
 
-template <typename TC>
-__global__ void __launch_bounds__(256, 4)
+// ONE: the products were not cut (S = 1, a prompt step): no batches of partial sums to hold,
+// fewer registers, more resident blocks.
+template <typename TC, bool ONE>
+__global__ void __launch_bounds__(256, ONE ? 8 : 4)
 latent_down_kernel(const float *__restrict__ P, int S, size_t stride, int ld, int q_col0, int q_rank,
                    const float *__restrict__ wq, int kv_col0, int kv_rank,
                    const float *__restrict__ wkv, int rot_dim, const float *__restrict__ cs,
@@ -48,12 +50,12 @@ latent_down_kernel(const float *__restrict__ P, int S, size_t stride, int ld, in
     float *zq = buf, *zc = buf + q_rank, *zr = zc + kv_rank;
     float sq = 0.0f, sc = 0.0f;
     for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
-        float v = add_partials(0.0f, p + q_col0 + i, S, stride);
+        float v = ONE ? p[q_col0 + i] : add_partials(0.0f, p + q_col0 + i, S, stride);
         zq[i] = v;
         sq = fmaf(v, v, sq);
     }
     for (int i = threadIdx.x; i < kv_rank + rot_dim; i += blockDim.x) {
-        float v = add_partials(0.0f, p + kv_col0 + i, S, stride);
+        float v = ONE ? p[kv_col0 + i] : add_partials(0.0f, p + kv_col0 + i, S, stride);
         zc[i] = v;
         if (i < kv_rank)
             sc = fmaf(v, v, sc);
@@ -366,16 +368,21 @@ extern "C" int jb_latent_down_rows(const float *P, int S, long long stride, int 
     size_t smem = (size_t)(q_rank + kv_rank + rot_dim) * 4;
     if (smem > 48 * 1024)
         return JB_EINVAL;
-    if (cache_dt == JB_F32)
-        launch(latent_down_kernel<float>, n, 256, smem, st, P, S, (size_t)stride, ld, q_col0, q_rank, wq,
-               kv_col0, kv_rank, wkv, rot_dim, cs, sn, rot_half, row_pos, row_seq, block_table,
-               bt_stride, (float *)cq_out, (float *)k_cache, (float *)rows_out, eps);
+#define JB_LD(TC, ONE)                                                                          \
+    launch(latent_down_kernel<TC, ONE>, n, 256, smem, st, P, S, (size_t)stride, ld, q_col0, q_rank, wq, \
+           kv_col0, kv_rank, wkv, rot_dim, cs, sn, rot_half, row_pos, row_seq, block_table,      \
+           bt_stride, (TC *)cq_out, (TC *)k_cache, (TC *)rows_out, eps)
+    if (cache_dt == JB_F32 && S == 1)
+        JB_LD(float, true);
+    else if (cache_dt == JB_F32)
+        JB_LD(float, false);
+    else if (cache_dt == JB_BF16 && S == 1)
+        JB_LD(bf16, true);
     else if (cache_dt == JB_BF16)
-        launch(latent_down_kernel<bf16>, n, 256, smem, st, P, S, (size_t)stride, ld, q_col0, q_rank, wq,
-               kv_col0, kv_rank, wkv, rot_dim, cs, sn, rot_half, row_pos, row_seq, block_table,
-               bt_stride, (bf16 *)cq_out, (bf16 *)k_cache, (bf16 *)rows_out, eps);
+        JB_LD(bf16, false);
     else
         return JB_EINVAL;
+#undef JB_LD
     return launch_status();
 }
 

@@ -64,8 +64,8 @@ DC = config(128, 300, [attn(4, 1, 64, 64, 0.11, window=130, softcap=50.0, q_temp
 # heads of 128, as many key/value heads as heads, a window of exactly a page, a temperature that
 # grows with every position, one latent head, no window on one layer, no repeated pass at all
 DD = config(96, 211, [attn(2, 2, 128, 128, 0.08, window=64, softcap=8.0, q_temp=(0.1, 1), ff=136),
-                      latent(1, 32, 16, 48, 64, 32, 0.15, ff=72),
-                      attn(2, 2, 128, 128, 0.08, softcap=30.0, ff=40)],
+                      latent(1, 24, 16, 40, 64, 32, 0.15, ff=72),
+                      attn(2, 2, 128, 128, 0.08, softcap=25.0, ff=40)],
             None, eps=3e-6, mult=1.3)
 
 CONFIGS = {"DA": DA, "DB": DB, "DC": DC, "DD": DD}

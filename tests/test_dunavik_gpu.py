@@ -48,8 +48,8 @@ def test_layer_norm(odt, n, dm):
     # two stacks of partial sums join the stream first, times a factor, in place
     a, c = rnd(3, n, dm, seed=3), rnd(2, n, dm, seed=4)
     xd = x.to(DEV).clone()
-    got = ops().layernorm(xd, w.to(DEV), b.to(DEV), 1e-5, torch.float32, a=a.to(DEV), b=c.to(DEV), mult=0.7).cpu()
-    xs = x + 0.7 * (a.sum(0) + c.sum(0))
+    got = ops().layernorm(xd, w.to(DEV), b.to(DEV), 1e-5, torch.float32, a=a.to(DEV), b=c.to(DEV), mult=0.6).cpu()
+    xs = x + 0.6 * (a.sum(0) + c.sum(0))
     assert torch.allclose(xd.cpu(), xs, atol=2e-6, rtol=1e-6)
     assert (got - pd.layer_norm(xs, w, b, 1e-5)).abs().max() <= 1e-5
     # one stack alone, and the add without a norm
@@ -211,7 +211,7 @@ def test_capped_sloped_window_attention(dtype, hd, vd, nh, nkv, window, cap):
 
 
 @pytest.mark.parametrize("hd,nh,nkv,window,cap", [(64, 4, 1, 130, 50.0), (64, 10, 5, 0, 20.0), (128, 2, 2, 64, 8.0),
-                                                   (128, 8, 2, 1000, 0.0), (128, 40, 2, 37, 30.0)])
+                                                   (128, 8, 2, 1000, 0.0), (128, 40, 2, 37, 25.0)])
 def test_capped_sloped_window_attention_on_the_tensor_cores(hd, nh, nkv, window, cap):
     dt = torch.bfloat16
     lens = [1, 300, 131, 520]
@@ -289,7 +289,7 @@ def rope_tables(base, dims, n_pos):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,D,R,dims,Dv,C,Cq", [(4, 16, 8, 8, 24, 40, 24), (3, 10, 6, 4, 6, 22, 14),
-                                                (2, 64, 32, 32, 64, 96, 48), (1, 32, 16, 16, 48, 64, 32)])
+                                                (2, 64, 32, 32, 64, 96, 48), (1, 24, 16, 16, 40, 64, 32)])
 def test_latent_attention_steps(dtype, H, D, R, dims, Dv, C, Cq):
     """The mixer's kernels in a row, from the products' sums to the gated heads, against the
     plain form that builds every head's keys and values: prompt rows of two sequences, then one
